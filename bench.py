@@ -1,0 +1,472 @@
+"""Benchmark of the AttnRes read (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2, "standard full-rank operator sweep"): packed BF16
+values [S, 16384, D] ~ N(0,1) for S in {2,5,9,17,25,49} x D in {1024,2048,4096},
+query [D] ~ N(0,0.02), R = D, upstream gradient ~ N(0,1).  One STEP is one
+forward and one backward of every one of the 18 cells: all forwards first, then
+all backwards in reverse order, as a network would run them; more than 25 GB of
+other traffic separates a cell's forward from its backward, so nothing is served
+from L2 between timed passes.
+
+With N > 1 (torchrun) every rank owns its own 16 384 positions of every cell
+(position sharding, no data-path collective; weak scaling) and the FP32 query
+gradient of every cell is all-reduced over NCCL before the BF16 cast.
+
+Printed JSON (rank 0, one line): whole-job tokens/s (`value`), the HBM roofline
+of the dominant (backward) kernel, the same metric end to end from pinned host
+buffers through the public `attnres()` API (`e2e`), the CPU oracle timed on the
+host cores (`cpu_baseline`) and the SM clocks sampled during the timed region.
+
+`--impl reference` times the reference's CPU definition of the path (the PyTorch
+oracle port, all host threads) on a bounded row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for entry in (ROOT, ROOT / "fast-attnres_b200"):
+    if str(entry) not in sys.path:
+        sys.path.insert(0, str(entry))
+
+import torch  # noqa: E402
+
+ROWS = 16384
+SOURCE_COUNTS = (2, 5, 9, 17, 25, 49)
+WIDTHS = (1024, 2048, 4096)
+CELLS = [(s, d) for d in WIDTHS for s in SOURCE_COUNTS]
+CPU_SAMPLE_ROWS = 512
+SEED = 20260827
+METRIC = "attnres_fwd_bwd_tokens_per_s"
+WORKLOAD = "config2_operator_sweep_packed_S{2,5,9,17,25,49}xD{1024,2048,4096}_N16384_R=D"
+
+
+def algorithmic_bytes(sources: int, rows: int, width: int) -> tuple[int, int]:
+    """(forward, backward) bytes per call: values read + output written; values and
+    upstream read + value gradients written.  Statistics, the dquery workspace and
+    the query itself are overhead and are not counted."""
+    forward = rows * (2 * sources * width + 2 * width)
+    backward = rows * (2 * sources * width + 2 * width + 2 * sources * width)
+    return forward, backward
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def traffic_ratio() -> float | None:
+    """DRAM bytes / algorithmic bytes of the backward kernel from the committed ncu
+    capture (profiles/dram_traffic.json), or None when no capture is recorded."""
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["backward"]["dram_over_algorithmic"])
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = index
+            if visible:
+                entries = [e.strip() for e in visible.split(",") if e.strip()]
+                if index < len(entries) and entries[index].isdigit():
+                    physical = int(entries[index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+
+    def _loop(self):
+        nv = self.nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml_unavailable"]}
+        ordered = sorted(self.samples)
+        return {"sm_mhz": ordered[len(ordered) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(ordered)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_oracle_tokens_per_s(rows: int, repeats: int = 1) -> tuple[float, float, int]:
+    """Forward+backward of the PyTorch oracle port on the host, every cell at `rows`
+    rows; returns (tokens/s, seconds of CPU work, threads)."""
+    from oracle import attnres_oracle as ao
+    generator = torch.Generator().manual_seed(SEED)
+    cases = []
+    for sources, width in CELLS:
+        values = torch.randn(sources, rows, width, generator=generator).to(torch.bfloat16)
+        query = (torch.randn(width, generator=generator) * 0.02).to(torch.bfloat16)
+        upstream = torch.randn(rows, width, generator=generator).to(torch.bfloat16)
+        cases.append((values, query, upstream))
+    ao.oracle_with_grads(*cases[0])  # warm the thread pool
+    start = time.perf_counter()
+    for _ in range(repeats):
+        for values, query, upstream in cases:
+            ao.oracle_with_grads(values, query, upstream)
+    seconds = time.perf_counter() - start
+    return repeats * len(CELLS) * rows / seconds, seconds, torch.get_num_threads()
+
+
+def run_reference_arm(args, rank: int) -> None:
+    if rank != 0:
+        return
+    rates, elapsed = [], 0.0
+    for _ in range(max(1, min(args.warmup, 2))):  # untimed passes
+        cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS)
+    for _ in range(args.steps):
+        rate, seconds, threads = cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS)
+        rates.append(rate)
+        elapsed += seconds
+    value = sum(rates) / len(rates)
+    sample = f"all 18 cells at {CPU_SAMPLE_ROWS} rows each per step (same S, D, R; rows reduced)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * elapsed / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 storage / fp32 arithmetic", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_step": CPU_SAMPLE_ROWS * len(CELLS)},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+class Cell:
+    """Device buffers and captured graphs of one (S, D) cell."""
+
+    def __init__(self, sources, width, device, generator, grad_buffer, out_buffer, upstream):
+        from attnres import _native
+        self.S, self.D, self.N = sources, width, ROWS
+        self.values = torch.randn(sources, ROWS, width, device=device, dtype=torch.bfloat16,
+                                  generator=generator)
+        self.query = (torch.randn(width, device=device, generator=generator) * 0.02).to(torch.bfloat16)
+        self.upstream = upstream
+        self.out = out_buffer[:ROWS * width].view(ROWS, width)
+        self.grad = grad_buffer[:sources * ROWS * width].view(sources, ROWS, width)
+        self.logits = torch.empty(sources, ROWS, device=device, dtype=torch.float32)
+        self.stats = torch.empty(2, ROWS, device=device, dtype=torch.float32)
+        self.partial_rows = _native.dq_workspace_rows(ROWS, sources, width, width, device.index)
+        self.partials = torch.empty(self.partial_rows, width, device=device, dtype=torch.float32)
+        self.dq32 = torch.empty(width, device=device, dtype=torch.float32)
+        self.dq = torch.empty(width, device=device, dtype=torch.bfloat16)
+        step = ROWS * width * 2
+        self.src_ptrs = [self.values.data_ptr() + s * step for s in range(sources)]
+        self.grad_ptrs = [self.grad.data_ptr() + s * step for s in range(sources)]
+        self.fwd_bytes, self.bwd_bytes = algorithmic_bytes(sources, ROWS, width)
+        self.fwd_graph = self.bwd_graph = None
+
+    def forward(self, stream):
+        from attnres import _native
+        _native.forward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, self.N, self.D,
+                        self.D, self.query.data_ptr(), 1, 2**-23, 1.0, self.out.data_ptr(), self.D,
+                        self.logits.data_ptr(), self.stats.data_ptr(), 0, stream)
+
+    def backward(self, stream, distributed):
+        from attnres import _native
+        _native.backward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, self.N, self.D,
+                         self.D, self.query.data_ptr(), 1, 2**-23, 1.0,
+                         self.upstream.data_ptr(), self.D, 1,
+                         self.logits.data_ptr(), self.stats.data_ptr(),
+                         self.grad_ptrs, [self.D] * self.S,
+                         self.partials.data_ptr(), self.partial_rows,
+                         None if distributed else self.dq.data_ptr(),
+                         self.dq32.data_ptr() if distributed else None, 0, stream)
+
+    def capture(self, distributed):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.forward(side.cuda_stream)
+            self.backward(side.cuda_stream, distributed)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.fwd_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.fwd_graph):
+            self.forward(torch.cuda.current_stream().cuda_stream)
+        self.bwd_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.bwd_graph):
+            self.backward(torch.cuda.current_stream().cuda_stream, distributed)
+
+
+def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
+    import torch.distributed as dist
+    from attnres import _native, attnres
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    _native.load()
+    generator = torch.Generator(device=device).manual_seed(SEED + rank)
+
+    max_elems = max(s * ROWS * d for s, d in CELLS)
+    grad_buffer = torch.empty(max_elems, device=device, dtype=torch.bfloat16)
+    out_buffer = torch.empty(ROWS * max(WIDTHS), device=device, dtype=torch.bfloat16)
+    upstreams = {d: torch.randn(ROWS, d, device=device, dtype=torch.bfloat16, generator=generator)
+                 for d in WIDTHS}
+    cells = [Cell(s, d, device, generator, grad_buffer, out_buffer, upstreams[d]) for s, d in CELLS]
+    for cell in cells:
+        cell.capture(distributed)
+    torch.cuda.synchronize()
+
+    def make_events():
+        return [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for _ in cells]
+
+    def step(fwd_events=None, bwd_events=None):
+        for index, cell in enumerate(cells):
+            if fwd_events:
+                fwd_events[index][0].record()
+            cell.fwd_graph.replay()
+            if fwd_events:
+                fwd_events[index][1].record()
+        for index in reversed(range(len(cells))):
+            cell = cells[index]
+            if bwd_events:
+                bwd_events[index][0].record()
+            cell.bwd_graph.replay()
+            if bwd_events:
+                bwd_events[index][1].record()
+            if distributed:
+                dist.all_reduce(cell.dq32)
+                cell.dq.copy_(cell.dq32)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    fwd_ms = [0.0] * len(cells)
+    bwd_ms = [0.0] * len(cells)
+    all_events = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            fe, be = make_events(), make_events()
+            step(fe, be)
+            all_events.append((fe, be))
+        stop.record()
+        barrier()
+    total_ms = start.elapsed_time(stop)
+    for fe, be in all_events:
+        for index in range(len(cells)):
+            fwd_ms[index] += fe[index][0].elapsed_time(fe[index][1]) / args.steps
+            bwd_ms[index] += be[index][0].elapsed_time(be[index][1]) / args.steps
+    if distributed:
+        worst = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        total_ms = float(worst.item())
+    ms_per_step = total_ms / args.steps
+    tokens_per_step = world * len(cells) * ROWS
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: pinned host buffers -> public API -> host results
+    e2e = run_e2e(args, cells, device, distributed)
+    if distributed:
+        worst = torch.tensor([e2e["ms_per_step"]], device=device, dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        e2e["ms_per_step"] = float(worst.item())
+    e2e_value = tokens_per_step / (e2e["ms_per_step"] * 1e-3)
+
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak_gbs()
+    bwd_bytes = sum(c.bwd_bytes for c in cells)
+    fwd_bytes = sum(c.fwd_bytes for c in cells)
+    bwd_gbs = bwd_bytes / (sum(bwd_ms) * 1e-3) / 1e9
+    fwd_gbs = fwd_bytes / (sum(fwd_ms) * 1e-3) / 1e9
+    both_gbs = (bwd_bytes + fwd_bytes) / ((sum(bwd_ms) + sum(fwd_ms)) * 1e-3) / 1e9
+    ratio = traffic_ratio()
+    per_cell = []
+    for cell, f, b in zip(cells, fwd_ms, bwd_ms):
+        per_cell.append({
+            "S": cell.S, "D": cell.D, "fwd_ms": round(f, 4), "bwd_ms": round(b, 4),
+            "tokens_per_s": round(ROWS / ((f + b) * 1e-3)),
+            "fwd_gbs": round(cell.fwd_bytes / (f * 1e-3) / 1e9, 1),
+            "bwd_gbs": round(cell.bwd_bytes / (b * 1e-3) / 1e9, 1),
+            "gbs": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9, 1),
+            "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
+        })
+    cpu_rate, cpu_seconds, threads = cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 storage / fp32 arithmetic", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "cells": len(cells),
+                   "layout": "packed", "parallelism": f"position-sharded x{world}",
+                   "cache": "25 GB of other cells' traffic between a cell's passes (>> 126 MB L2)",
+                   "timing": "CUDA events around per-cell CUDA-graph replays"},
+        "gbs_fwd_bwd": both_gbs * world, "frac_of_peak_fwd_bwd": both_gbs / peak,
+        "frac_of_nominal_8TBs": both_gbs / 8000.0,
+        "roofline": {"bound": "hbm", "kernel": "backward (dominant: 2/3 of the bytes)",
+                     "achieved": bwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": bwd_gbs / peak,
+                     "traffic": None if ratio is None else ratio * bwd_bytes / len(cells),
+                     "algorithmic_bytes_per_launch": bwd_bytes / len(cells),
+                     "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak}},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e["ms_per_step"],
+                "steps": e2e["steps"]},
+        "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"PyTorch oracle port, all 18 cells at {CPU_SAMPLE_ROWS} rows "
+                                   f"each ({cpu_seconds:.1f} s of CPU work)"},
+        "gpu_launches": args.steps * len(cells) * 3,
+        "clocks": clocks.summary(),
+        "cells": per_cell,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_e2e(args, cells, device, distributed) -> dict:
+    """The same sweep through `attnres()` + autograd with every input starting in pinned
+    host memory and every result (out, value gradients, query gradient) copied back."""
+    import torch.distributed as dist
+    from attnres import attnres
+    steps = max(1, min(args.steps, 3))
+    max_elems = max(c.S * ROWS * c.D for c in cells)
+    host_values = torch.empty(max_elems, dtype=torch.bfloat16).pin_memory()
+    host_grads = torch.empty(max_elems, dtype=torch.bfloat16).pin_memory()
+    host_up = torch.empty(ROWS * max(WIDTHS), dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(ROWS * max(WIDTHS), dtype=torch.bfloat16).pin_memory()
+    host_query = torch.empty(max(WIDTHS), dtype=torch.bfloat16).pin_memory()
+    host_dq = torch.empty(max(WIDTHS), dtype=torch.bfloat16).pin_memory()
+    host_values.normal_()
+    host_up.normal_()
+    host_query.normal_(std=0.02)
+    h2d = d2h = 0
+
+    def one_step(count):
+        nonlocal h2d, d2h
+        for cell in cells:
+            n_values = cell.S * ROWS * cell.D
+            values = host_values[:n_values].view(cell.S, ROWS, cell.D).to(device, non_blocking=True)
+            query = host_query[:cell.D].to(device, non_blocking=True)
+            upstream = host_up[:ROWS * cell.D].view(ROWS, cell.D).to(device, non_blocking=True)
+            values.requires_grad_()
+            query.requires_grad_()
+            out = attnres(values, query)
+            dv, dq = torch.autograd.grad(out, (values, query), upstream)
+            if distributed:
+                dq32 = dq.float()
+                dist.all_reduce(dq32)
+                dq = dq32.to(torch.bfloat16)
+            host_out[:ROWS * cell.D].view(ROWS, cell.D).copy_(out, non_blocking=True)
+            host_grads[:n_values].view(cell.S, ROWS, cell.D).copy_(dv, non_blocking=True)
+            host_dq[:cell.D].copy_(dq, non_blocking=True)
+            if count:
+                h2d += 2 * (n_values + cell.D + ROWS * cell.D)
+                d2h += 2 * (n_values + cell.D + ROWS * cell.D)
+            del values, query, upstream, out, dv, dq
+
+    one_step(False)
+    if distributed:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for index in range(steps):
+        one_step(index == 0)
+    stop.record()
+    if distributed:
+        dist.barrier()
+    torch.cuda.synchronize()
+    return {"ms_per_step": start.elapsed_time(stop) / steps, "h2d": h2d, "d2h": d2h, "steps": steps}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU fallback")
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_gpu_arm(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

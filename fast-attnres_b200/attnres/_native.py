@@ -1,0 +1,115 @@
+"""ctypes binding of ``libattnres_b200.so`` (C ABI: include/attnres_b200.h).
+
+There is no fallback: if the library is missing or the wrong version, every
+call raises.  Build it with ``python fast-attnres_b200/build.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_uint32, c_void_p
+from pathlib import Path
+
+ABI_VERSION = 1
+FLAG_FORCE_GENERIC = 1
+LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / "libattnres_b200.so"
+
+_PTR_ARRAY = ctypes.POINTER(c_void_p)
+_I64_ARRAY = ctypes.POINTER(c_int64)
+
+# name -> (restype, argtypes); one entry per declaration in include/attnres_b200.h
+SIGNATURES = {
+    "attnres_b200_abi_version": (c_int32, []),
+    "attnres_b200_status_string": (c_char_p, [c_int32]),
+    "attnres_b200_kernel_family": (c_char_p, [c_int32, c_int32, c_int32, c_int32, c_int32]),
+    "attnres_b200_dq_workspace_rows": (c_int32, [c_int64, c_int32, c_int32, c_int32, c_int32]),
+    "attnres_b200_forward": (c_int32, [
+        _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
+        c_int32, c_int64, c_int32, c_int32,
+        c_void_p, c_int64, c_float, c_float,
+        c_void_p, c_int64, c_void_p, c_void_p,
+        c_uint32, c_void_p]),
+    "attnres_b200_backward": (c_int32, [
+        _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
+        c_int32, c_int64, c_int32, c_int32,
+        c_void_p, c_int64, c_float, c_float,
+        c_void_p, c_int64, c_int64,
+        c_void_p, c_void_p,
+        _PTR_ARRAY, _I64_ARRAY,
+        c_void_p, c_int32,
+        c_void_p, c_void_p,
+        c_uint32, c_void_p]),
+}
+
+_library = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and check its ABI version."""
+    global _library
+    if _library is not None:
+        return _library
+    if not LIBRARY_PATH.exists():
+        raise RuntimeError(
+            f"{LIBRARY_PATH} is missing: the sm_100a CUDA library has not been built "
+            "(run `python fast-attnres_b200/build.py`); there is no fallback path")
+    library = ctypes.CDLL(str(LIBRARY_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        function = getattr(library, name)
+        function.restype = restype
+        function.argtypes = argtypes
+    found = library.attnres_b200_abi_version()
+    if found != ABI_VERSION:
+        raise RuntimeError(f"libattnres_b200.so has ABI {found}, binding expects {ABI_VERSION}")
+    _library = library
+    return library
+
+
+def status_text(status: int) -> str:
+    return load().attnres_b200_status_string(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise RuntimeError(f"{what} failed: {status_text(status)} (status {status})")
+
+
+def pointer_array(addresses) -> ctypes.Array:
+    return (c_void_p * len(addresses))(*addresses)
+
+
+def int64_array(values) -> ctypes.Array:
+    return (c_int64 * len(values))(*values)
+
+
+def forward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_stride,
+            eps, scale, out_ptr, out_row_stride, logits_ptr, stats_ptr, flags, stream) -> None:
+    status = load().attnres_b200_forward(
+        pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
+        S, N, D, R, query_ptr, query_stride, eps, scale,
+        out_ptr, out_row_stride, logits_ptr, stats_ptr, flags, stream)
+    check(status, "attnres_b200_forward")
+
+
+def dq_workspace_rows(N, S, D, R, device_index) -> int:
+    rows = load().attnres_b200_dq_workspace_rows(N, S, D, R, device_index)
+    if rows < 0:
+        check(-rows, "attnres_b200_dq_workspace_rows")
+    return rows
+
+
+def backward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_stride,
+             eps, scale, go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
+             dsrc_ptrs, dsrc_row_strides, partials_ptr, partial_rows,
+             dq_bf16_ptr, dq_f32_ptr, flags, stream) -> None:
+    status = load().attnres_b200_backward(
+        pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
+        S, N, D, R, query_ptr, query_stride, eps, scale,
+        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
+        None if dsrc_ptrs is None else pointer_array(dsrc_ptrs),
+        None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
+        partials_ptr, partial_rows, dq_bf16_ptr, dq_f32_ptr, flags, stream)
+    check(status, "attnres_b200_backward")
+
+
+def kernel_family(S, D, R, aligned, backward_pass) -> str:
+    return load().attnres_b200_kernel_family(S, D, R, int(aligned), int(backward_pass)).decode()

@@ -1,0 +1,287 @@
+// C ABI of the sm_100a AttnRes read kernels (declared in include/attnres_b200.h):
+// host-side argument checks, kernel-family selection and launches.
+#include "../../include/attnres_b200.h"
+
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+#include "generic_kernels.cuh"
+#include "tma_kernels.cuh"
+
+namespace attnres_b200 {
+namespace {
+
+int sm_count(int device, int* out) {
+  // Queried per call: the attribute lookup is a cached driver read and keeps
+  // the library free of mutable global state.
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+      sms < 1) {
+    cudaGetLastError();
+    return ATTNRES_B200_ERR_CUDA;
+  }
+  *out = sms;
+  return ATTNRES_B200_OK;
+}
+
+int current_device(int* device) {
+  if (cudaGetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return ATTNRES_B200_ERR_CUDA;
+  }
+  return ATTNRES_B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool aligned2(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1u) == 0; }
+
+int check_shape(int32_t S, int64_t N, int32_t D, int32_t R) {
+  if (S < 1 || S > kMaxSources) return ATTNRES_B200_ERR_BAD_SOURCE_COUNT;
+  if (D < 1 || D > kMaxWidth) return ATTNRES_B200_ERR_BAD_WIDTH;
+  if (R < 1 || R > D) return ATTNRES_B200_ERR_BAD_RANK;
+  if (N < 1) return ATTNRES_B200_ERR_BAD_ROWS;
+  return ATTNRES_B200_OK;
+}
+
+int check_scalars(float eps, float scale) {
+  if (!std::isfinite(eps) || eps <= 0.f || !std::isfinite(scale)) return ATTNRES_B200_ERR_BAD_SCALAR;
+  return ATTNRES_B200_OK;
+}
+
+// Fills the by-value table and reports whether every source allows 16-byte
+// accesses along the feature axis.
+int fill_sources(SourceTable& t, const void* const* ptrs, const int64_t* rs, const int64_t* fs,
+                 int S, int64_t N, bool* vec_ok) {
+  bool ok = true;
+  for (int s = 0; s < S; ++s) {
+    if (ptrs[s] == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+    if (!aligned2(ptrs[s])) return ATTNRES_B200_ERR_MISALIGNED;
+    t.ptr[s] = static_cast<const __nv_bfloat16*>(ptrs[s]);
+    t.row_stride[s] = rs[s];
+    t.feat_stride[s] = fs[s];
+    ok = ok && aligned16(ptrs[s]) && fs[s] == 1 && (N == 1 || rs[s] % 8 == 0);
+  }
+  for (int s = S; s < kMaxSources; ++s) {
+    t.ptr[s] = nullptr;
+    t.row_stride[s] = 0;
+    t.feat_stride[s] = 0;
+  }
+  *vec_ok = ok;
+  return ATTNRES_B200_OK;
+}
+
+template <int VEC, int NJ, int T, int B>
+int launch_fwd_generic(const FwdParams& p, int grid, cudaStream_t stream) {
+  fwd_generic_kernel<VEC, NJ, T, B><<<grid, T, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
+}
+
+template <int VEC, int NJ, int T, int B>
+int launch_bwd_generic(const BwdParams& p, int grid, cudaStream_t stream) {
+  bwd_generic_kernel<VEC, NJ, T, B><<<grid, T, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
+}
+
+int dispatch_fwd_generic(const FwdParams& p, bool vec, int grid, cudaStream_t st) {
+  const int D = p.D;
+  if (vec) {
+    if (D <= 1024) return launch_fwd_generic<8, 1, 128, 4>(p, grid, st);
+    if (D <= 2048) return launch_fwd_generic<8, 1, 256, 4>(p, grid, st);
+    if (D <= 4096) return launch_fwd_generic<8, 2, 256, 4>(p, grid, st);
+    return launch_fwd_generic<8, 4, 256, 2>(p, grid, st);
+  }
+  if (D <= 256) return launch_fwd_generic<1, 1, 256, 4>(p, grid, st);
+  if (D <= 512) return launch_fwd_generic<1, 2, 256, 4>(p, grid, st);
+  if (D <= 1024) return launch_fwd_generic<1, 4, 256, 4>(p, grid, st);
+  if (D <= 2048) return launch_fwd_generic<1, 8, 256, 4>(p, grid, st);
+  if (D <= 4096) return launch_fwd_generic<1, 16, 256, 4>(p, grid, st);
+  return launch_fwd_generic<1, 32, 256, 2>(p, grid, st);
+}
+
+int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st) {
+  const int D = p.D;
+  if (vec) {
+    if (D <= 1024) return launch_bwd_generic<8, 1, 128, 4>(p, grid, st);
+    if (D <= 2048) return launch_bwd_generic<8, 1, 256, 4>(p, grid, st);
+    if (D <= 4096) return launch_bwd_generic<8, 2, 256, 4>(p, grid, st);
+    return launch_bwd_generic<8, 4, 256, 2>(p, grid, st);
+  }
+  if (D <= 256) return launch_bwd_generic<1, 1, 256, 4>(p, grid, st);
+  if (D <= 512) return launch_bwd_generic<1, 2, 256, 4>(p, grid, st);
+  if (D <= 1024) return launch_bwd_generic<1, 4, 256, 4>(p, grid, st);
+  if (D <= 2048) return launch_bwd_generic<1, 8, 256, 4>(p, grid, st);
+  if (D <= 4096) return launch_bwd_generic<1, 16, 256, 4>(p, grid, st);
+  return launch_bwd_generic<1, 32, 256, 2>(p, grid, st);
+}
+
+constexpr int kWorkspaceRowsPerSm = 8;
+
+}  // namespace
+}  // namespace attnres_b200
+
+using namespace attnres_b200;
+
+extern "C" int attnres_b200_abi_version(void) { return ATTNRES_B200_ABI_VERSION; }
+
+extern "C" const char* attnres_b200_status_string(int status) {
+  switch (status) {
+    case ATTNRES_B200_OK: return "ok";
+    case ATTNRES_B200_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case ATTNRES_B200_ERR_BAD_SOURCE_COUNT: return "source count outside 1..129";
+    case ATTNRES_B200_ERR_BAD_WIDTH: return "value width outside 1..8192";
+    case ATTNRES_B200_ERR_BAD_RANK: return "query rank outside 1..D";
+    case ATTNRES_B200_ERR_BAD_ROWS: return "row count must be positive";
+    case ATTNRES_B200_ERR_BAD_SCALAR: return "eps must be finite and positive, scale finite";
+    case ATTNRES_B200_ERR_MISALIGNED: return "a BF16 pointer is not 2-byte aligned";
+    case ATTNRES_B200_ERR_WORKSPACE: return "dquery workspace has too few rows";
+    case ATTNRES_B200_ERR_CUDA: return "a CUDA runtime call failed";
+    case ATTNRES_B200_ERR_BAD_FLAGS: return "unknown flag bits";
+    case ATTNRES_B200_ERR_NOTHING_TO_DO: return "backward needs a value or a query gradient output";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R,
+                                                  int32_t aligned, int32_t backward) {
+  if (check_shape(S, 1, D, R) != ATTNRES_B200_OK) return "invalid";
+  if (!aligned) return "generic";
+  if (backward) return tma_bwd_supported(S, D, R) ? "tma" : "generic";
+  return tma_fwd_supported(S, D, R) ? "tma" : "generic";
+}
+
+extern "C" int attnres_b200_forward(
+    const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    void* out, int64_t out_row_stride,
+    float* logits, float* stats,
+    uint32_t flags, void* stream) {
+  if (int st = check_shape(S, N, D, R)) return st;
+  if (int st = check_scalars(eps, scale)) return st;
+  if (flags & ~ATTNRES_B200_FLAG_FORCE_GENERIC) return ATTNRES_B200_ERR_BAD_FLAGS;
+  if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !out || !logits || !stats)
+    return ATTNRES_B200_ERR_NULL_POINTER;
+  if (!aligned2(query) || !aligned2(out)) return ATTNRES_B200_ERR_MISALIGNED;
+
+  FwdParams p;
+  bool vec = false;
+  if (int st = fill_sources(p.src, src_ptrs, src_row_stride, src_feat_stride, S, N, &vec)) return st;
+  p.S = S;
+  p.D = D;
+  p.R = R;
+  p.N = N;
+  p.query = static_cast<const __nv_bfloat16*>(query);
+  p.query_stride = query_stride;
+  p.eps = eps;
+  p.scale = scale;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_row_stride = out_row_stride;
+  p.logits = logits;
+  p.stats = stats;
+  vec = vec && D % 8 == 0 && aligned16(out) && (N == 1 || out_row_stride % 8 == 0);
+
+  int device = 0, sms = 0;
+  if (int st = current_device(&device)) return st;
+  if (int st = sm_count(device, &sms)) return st;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+
+  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC) && tma_fwd_supported(S, D, R))
+    return launch_fwd_tma(p, sms, cs);
+
+  const int64_t cap = (int64_t)sms * 16;
+  const int grid = (int)(N < cap ? N : cap);
+  return dispatch_fwd_generic(p, vec, grid, cs);
+}
+
+extern "C" int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t R,
+                                                  int32_t device) {
+  if (int st = check_shape(S, N, D, R)) return -st;
+  int sms = 0;
+  if (int st = sm_count(device, &sms)) return -st;
+  const int64_t cap = (int64_t)sms * kWorkspaceRowsPerSm;
+  return (int32_t)(N < cap ? N : cap);
+}
+
+extern "C" int attnres_b200_backward(
+    const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
+    const float* logits, const float* stats,
+    void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
+    float* dq_partials, int32_t dq_partial_rows,
+    void* dq_bf16, float* dq_f32,
+    uint32_t flags, void* stream) {
+  if (int st = check_shape(S, N, D, R)) return st;
+  if (int st = check_scalars(eps, scale)) return st;
+  if (flags & ~ATTNRES_B200_FLAG_FORCE_GENERIC) return ATTNRES_B200_ERR_BAD_FLAGS;
+  if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !grad_out || !logits || !stats)
+    return ATTNRES_B200_ERR_NULL_POINTER;
+  const bool want_dq = dq_bf16 != nullptr || dq_f32 != nullptr;
+  const bool want_dv = dsrc_ptrs != nullptr;
+  if (!want_dq && !want_dv) return ATTNRES_B200_ERR_NOTHING_TO_DO;
+  if (want_dv && dsrc_row_stride == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  if (want_dq && dq_partials == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  if (!aligned2(query) || !aligned2(grad_out) || (dq_bf16 && !aligned2(dq_bf16)))
+    return ATTNRES_B200_ERR_MISALIGNED;
+
+  BwdParams p;
+  bool vec = false;
+  if (int st = fill_sources(p.src, src_ptrs, src_row_stride, src_feat_stride, S, N, &vec)) return st;
+  for (int s = 0; s < kMaxSources; ++s) {
+    p.grad.ptr[s] = nullptr;
+    p.grad.row_stride[s] = 0;
+  }
+  if (want_dv) {
+    for (int s = 0; s < S; ++s) {
+      if (dsrc_ptrs[s] == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+      if (!aligned2(dsrc_ptrs[s])) return ATTNRES_B200_ERR_MISALIGNED;
+      p.grad.ptr[s] = static_cast<__nv_bfloat16*>(dsrc_ptrs[s]);
+      p.grad.row_stride[s] = dsrc_row_stride[s];
+      vec = vec && aligned16(dsrc_ptrs[s]) && (N == 1 || dsrc_row_stride[s] % 8 == 0);
+    }
+  }
+  p.S = S;
+  p.D = D;
+  p.R = R;
+  p.write_dv = want_dv ? 1 : 0;
+  p.N = N;
+  p.query = static_cast<const __nv_bfloat16*>(query);
+  p.query_stride = query_stride;
+  p.eps = eps;
+  p.scale = scale;
+  p.grad_out = static_cast<const __nv_bfloat16*>(grad_out);
+  p.go_row_stride = go_row_stride;
+  p.go_feat_stride = go_feat_stride;
+  p.logits = logits;
+  p.stats = stats;
+  p.dq_partials = want_dq ? dq_partials : nullptr;
+  vec = vec && D % 8 == 0 && aligned16(grad_out) && go_feat_stride == 1 &&
+        (N == 1 || go_row_stride % 8 == 0);
+
+  int device = 0, sms = 0;
+  if (int st = current_device(&device)) return st;
+  if (int st = sm_count(device, &sms)) return st;
+  const int64_t cap = (int64_t)sms * kWorkspaceRowsPerSm;
+  const int max_rows = (int)(N < cap ? N : cap);
+  if (want_dq && dq_partial_rows < max_rows) return ATTNRES_B200_ERR_WORKSPACE;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+
+  int grid = max_rows;
+  int st;
+  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC) && tma_bwd_supported(S, D, R)) {
+    st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
+  } else {
+    st = dispatch_bwd_generic(p, vec, grid, cs);
+  }
+  if (st != ATTNRES_B200_OK) return st;
+  if (want_dq) {
+    dq_reduce_kernel<<<(R + 31) / 32, 256, 0, cs>>>(dq_partials, grid, R,
+                                                    static_cast<__nv_bfloat16*>(dq_bf16), dq_f32);
+    if (cudaGetLastError() != cudaSuccess) return ATTNRES_B200_ERR_CUDA;
+  }
+  return ATTNRES_B200_OK;
+}

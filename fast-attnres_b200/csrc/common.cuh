@@ -1,0 +1,110 @@
+// Shared definitions for the sm_100a AttnRes read kernels: the by-value source
+// tables, kernel parameter blocks and small device helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace attnres_b200 {
+
+constexpr int kMaxSources = 129;  // src/attnres/_sources.py:12
+constexpr int kMaxWidth = 8192;   // src/attnres/_sources.py:13
+
+// One record per source, passed BY VALUE inside the kernel parameter block
+// (3 096 bytes).  The reference selects the source pointer with a chain of
+// `tl.where` over a tuple of tensor arguments
+// (src/attnres/_kernels/fla_full_sources.py:253-282); a parameter-space table
+// needs no device allocation, no host-to-device copy and is frozen into a CUDA
+// graph node at capture time.
+struct SourceTable {
+  const __nv_bfloat16* ptr[kMaxSources];
+  int64_t row_stride[kMaxSources];   // elements
+  int64_t feat_stride[kMaxSources];  // elements
+};
+
+// Per-source gradient outputs: rows of D contiguous BF16 values.
+struct GradTable {
+  __nv_bfloat16* ptr[kMaxSources];
+  int64_t row_stride[kMaxSources];  // elements
+};
+
+struct FwdParams {
+  SourceTable src;
+  int32_t S;
+  int32_t D;
+  int32_t R;
+  int64_t N;
+  const __nv_bfloat16* query;
+  int64_t query_stride;
+  float eps;
+  float scale;
+  __nv_bfloat16* out;
+  int64_t out_row_stride;
+  float* logits;  // [S,N]
+  float* stats;   // [2,N]: max, 1/denominator
+};
+
+struct BwdParams {
+  SourceTable src;
+  GradTable grad;
+  int32_t S;
+  int32_t D;
+  int32_t R;
+  int32_t write_dv;  // 0: skip the value-gradient stores
+  int64_t N;
+  const __nv_bfloat16* query;
+  int64_t query_stride;
+  float eps;
+  float scale;
+  const __nv_bfloat16* grad_out;
+  int64_t go_row_stride;
+  int64_t go_feat_stride;
+  const float* logits;
+  const float* stats;
+  float* dq_partials;  // [gridDim.x, R]
+};
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+// The two BF16 halves of a packed 32-bit word (element 0 is the low half).
+__device__ __forceinline__ float bf16x2_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16x2_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  f[0] = bf16x2_lo(raw.x);
+  f[1] = bf16x2_hi(raw.x);
+  f[2] = bf16x2_lo(raw.y);
+  f[3] = bf16x2_hi(raw.y);
+  f[4] = bf16x2_lo(raw.z);
+  f[5] = bf16x2_hi(raw.z);
+  f[6] = bf16x2_lo(raw.w);
+  f[7] = bf16x2_hi(raw.w);
+}
+
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 r;
+  r.x = pack_bf16x2(f[0], f[1]);
+  r.y = pack_bf16x2(f[2], f[3]);
+  r.z = pack_bf16x2(f[4], f[5]);
+  r.w = pack_bf16x2(f[6], f[7]);
+  return r;
+}
+
+// Butterfly sum: every lane ends with the same value, in an order that depends
+// only on the lane layout (so results are reproducible run to run).
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace attnres_b200

@@ -1,0 +1,350 @@
+// Layout-generic AttnRes read kernels: any row / feature stride, any width
+// 1..8192, any base alignment, 64-bit offsets.  One CTA walks rows; each thread
+// owns NJ chunks of VEC consecutive features (VEC = 8 uses 16-byte accesses and
+// needs the aligned layout, VEC = 1 is element-wise).  These kernels cover what
+// the TMA-staged family does not take and are the cross-check for it.
+//
+// Equations follow validation/oracle.py:13-19 (forward) and the closed-form
+// gradient the reference kernels use (src/attnres/_kernels/fixed_tail.py:606-864).
+#pragma once
+
+#include "common.cuh"
+
+namespace attnres_b200 {
+
+// Loads the calling thread's NJ*VEC features of one row as FP32 (zero beyond D).
+template <int VEC, int NJ, int T>
+__device__ __forceinline__ void load_row(float* dst, const __nv_bfloat16* base,
+                                         int64_t feat_stride, int D, int tid) {
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int c = j * T + tid;
+    if constexpr (VEC == 8) {
+      if (c * 8 < D) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)c * 8));
+        unpack8(raw, dst + j * 8);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[j * 8 + e] = 0.f;
+      }
+    } else {
+      const unsigned short* b16 = reinterpret_cast<const unsigned short*>(base);
+      dst[j] = (c < D) ? bf16_bits_to_float(__ldg(b16 + (int64_t)c * feat_stride)) : 0.f;
+    }
+  }
+}
+
+// Sums K per-thread values over the CTA.  `scratch` is [2][K][T/32]; the
+// caller flips `parity` on every call so consecutive reductions use alternate
+// halves and need a single barrier each.  Warps are added in index order.
+template <int K, int T>
+__device__ __forceinline__ void block_sum(float* vals, float* scratch, int& parity, int tid) {
+  constexpr int NW = T / 32;
+  const int lane = tid & 31, warp = tid >> 5;
+  float* buf = scratch + parity * (K * NW);
+#pragma unroll
+  for (int k = 0; k < K; ++k) vals[k] = warp_sum(vals[k]);
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) buf[k * NW + warp] = vals[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) t += buf[k * NW + w];
+    vals[k] = t;
+  }
+  parity ^= 1;
+}
+
+template <int VEC, int NJ, int T, int B>
+__global__ void __launch_bounds__(T)
+fwd_generic_kernel(const __grid_constant__ FwdParams p) {
+  constexpr int NE = VEC * NJ;
+  constexpr int NW = T / 32;
+  __shared__ float scratch[2 * 2 * B * NW];
+  const int tid = threadIdx.x;
+  const int D = p.D, S = p.S, tail0 = p.D - p.R;
+  const float rank_f = (float)p.R;
+
+  // Query lanes owned by this thread (zero outside the tail), loaded once.
+  float q[NE];
+  uint32_t tailmask = 0;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const int d = (j * T + tid) * VEC + e;
+      const bool in_tail = d < D && d >= tail0;
+      q[j * VEC + e] = in_tail ? __bfloat162float(p.query[(int64_t)(d - tail0) * p.query_stride])
+                               : 0.f;
+      if (in_tail) tailmask |= 1u << (j * VEC + e);
+    }
+  }
+
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < p.N; row += gridDim.x) {
+    float acc[NE];
+#pragma unroll
+    for (int i = 0; i < NE; ++i) acc[i] = 0.f;
+    float run_max = -INFINITY, run_sum = 0.f;
+
+    for (int s0 = 0; s0 < S; s0 += B) {
+      float v[B][NE];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const int s = s0 + b;
+        if (s < S) {
+          load_row<VEC, NJ, T>(v[b], p.src.ptr[s] + row * p.src.row_stride[s],
+                               p.src.feat_stride[s], D, tid);
+        } else {
+#pragma unroll
+          for (int i = 0; i < NE; ++i) v[b][i] = 0.f;
+        }
+      }
+      // part[2b] = sum of squares over the tail, part[2b+1] = tail . query
+      float part[2 * B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        float ss = 0.f, dt = 0.f;
+#pragma unroll
+        for (int i = 0; i < NE; ++i) {
+          const float x = v[b][i];
+          dt = fmaf(x, q[i], dt);
+          if ((tailmask >> i) & 1u) ss = fmaf(x, x, ss);
+        }
+        part[2 * b] = ss;
+        part[2 * b + 1] = dt;
+      }
+      block_sum<2 * B, T>(part, scratch, parity, tid);
+
+      float z[B];
+      float new_max = run_max;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (s0 + b < S) {
+          const float inv_rms = rsqrtf(part[2 * b] / rank_f + p.eps);
+          z[b] = part[2 * b + 1] * inv_rms * p.scale;
+          new_max = fmaxf(new_max, z[b]);
+        } else {
+          z[b] = -INFINITY;
+        }
+      }
+      const float rescale = __expf(run_max - new_max);
+      run_sum *= rescale;
+#pragma unroll
+      for (int i = 0; i < NE; ++i) acc[i] *= rescale;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (s0 + b < S) {
+          const float w = __expf(z[b] - new_max);
+          run_sum += w;
+#pragma unroll
+          for (int i = 0; i < NE; ++i) acc[i] = fmaf(w, v[b][i], acc[i]);
+          if (tid == 0) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
+        }
+      }
+      run_max = new_max;
+    }
+
+    if (tid == 0) {
+      p.stats[row] = run_max;
+      p.stats[p.N + row] = 1.0f / run_sum;
+    }
+    __nv_bfloat16* orow = p.out + row * p.out_row_stride;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int c = j * T + tid;
+      if constexpr (VEC == 8) {
+        if (c * 8 < D) {
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = acc[j * 8 + e] / run_sum;
+          *reinterpret_cast<uint4*>(orow + (int64_t)c * 8) = pack8(o);
+        }
+      } else {
+        if (c < D) orow[c] = __float2bfloat16_rn(acc[j] / run_sum);
+      }
+    }
+  }
+}
+
+template <int VEC, int NJ, int T, int B>
+__global__ void __launch_bounds__(T)
+bwd_generic_kernel(const __grid_constant__ BwdParams p) {
+  constexpr int NE = VEC * NJ;
+  constexpr int NW = T / 32;
+  __shared__ float scratch[2 * 2 * B * NW];
+  __shared__ float s_dw[kMaxSources];   // sum_d v_s * dO
+  __shared__ float s_ir[kMaxSources];   // inverse RMS of the tail key
+  __shared__ float c_p[kMaxSources];    // softmax probability
+  __shared__ float c_a[kMaxSources];    // inv_rms * scale * dlogit
+  __shared__ float c_b[kMaxSources];    // inv_rms^2 * dlogit * logit / R
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int D = p.D, S = p.S, tail0 = p.D - p.R;
+  const float rank_f = (float)p.R;
+
+  float q[NE], dq[NE];
+  uint32_t tailmask = 0;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const int d = (j * T + tid) * VEC + e;
+      const bool in_tail = d < D && d >= tail0;
+      q[j * VEC + e] = in_tail ? __bfloat162float(p.query[(int64_t)(d - tail0) * p.query_stride])
+                               : 0.f;
+      dq[j * VEC + e] = 0.f;
+      if (in_tail) tailmask |= 1u << (j * VEC + e);
+    }
+  }
+
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < p.N; row += gridDim.x) {
+    float g[NE];
+    load_row<VEC, NJ, T>(g, p.grad_out + row * p.go_row_stride, p.go_feat_stride, D, tid);
+
+    // Sweep 1: per-source dot with the upstream gradient and tail sum of squares.
+    for (int s0 = 0; s0 < S; s0 += B) {
+      float part[2 * B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const int s = s0 + b;
+        float ss = 0.f, dw = 0.f;
+        if (s < S) {
+          float v[NE];
+          load_row<VEC, NJ, T>(v, p.src.ptr[s] + row * p.src.row_stride[s],
+                               p.src.feat_stride[s], D, tid);
+#pragma unroll
+          for (int i = 0; i < NE; ++i) {
+            dw = fmaf(v[i], g[i], dw);
+            if ((tailmask >> i) & 1u) ss = fmaf(v[i], v[i], ss);
+          }
+        }
+        part[2 * b] = ss;
+        part[2 * b + 1] = dw;
+      }
+      block_sum<2 * B, T>(part, scratch, parity, tid);
+      if (tid == 0) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          if (s0 + b < S) {
+            s_ir[s0 + b] = rsqrtf(part[2 * b] / rank_f + p.eps);
+            s_dw[s0 + b] = part[2 * b + 1];
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    // delta = sum_s p_s * dw_s (equal to sum_d dO*O), then per-source coefficients.
+    if (warp == 0) {
+      const float row_max = p.stats[row];
+      const float inv_sum = p.stats[p.N + row];
+      constexpr int KS = (kMaxSources + 31) / 32;
+      float prob[KS], zl[KS];
+      float local = 0.f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        const int s = lane + 32 * k;
+        prob[k] = 0.f;
+        zl[k] = 0.f;
+        if (s < S) {
+          zl[k] = p.logits[(int64_t)s * p.N + row];
+          prob[k] = __expf(zl[k] - row_max) * inv_sum;
+          local = fmaf(prob[k], s_dw[s], local);
+        }
+      }
+      const float delta = warp_sum(local);
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        const int s = lane + 32 * k;
+        if (s < S) {
+          const float dz = prob[k] * (s_dw[s] - delta);
+          const float ir = s_ir[s];
+          c_p[s] = prob[k];
+          c_a[s] = ir * p.scale * dz;
+          c_b[s] = ir * ir * dz * zl[k] / rank_f;
+        }
+      }
+    }
+    __syncthreads();
+
+    // Sweep 2: value gradients and the thread's share of the query gradient.
+    for (int s = 0; s < S; ++s) {
+      const float ps = c_p[s], ca = c_a[s], cb = c_b[s];
+      float v[NE];
+      if (tailmask != 0u) {
+        load_row<VEC, NJ, T>(v, p.src.ptr[s] + row * p.src.row_stride[s],
+                             p.src.feat_stride[s], D, tid);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NE; ++i) v[i] = 0.f;
+      }
+      float dv[NE];
+#pragma unroll
+      for (int i = 0; i < NE; ++i) {
+        float x = ps * g[i];
+        if ((tailmask >> i) & 1u) {
+          x += fmaf(ca, q[i], -cb * v[i]);
+          dq[i] = fmaf(ca, v[i], dq[i]);
+        }
+        dv[i] = x;
+      }
+      if (p.write_dv) {
+        __nv_bfloat16* grow = p.grad.ptr[s] + row * p.grad.row_stride[s];
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          const int c = j * T + tid;
+          if constexpr (VEC == 8) {
+            if (c * 8 < D) *reinterpret_cast<uint4*>(grow + (int64_t)c * 8) = pack8(dv + j * 8);
+          } else {
+            if (c < D) grow[c] = __float2bfloat16_rn(dv[j]);
+          }
+        }
+      }
+    }
+  }
+
+  if (p.dq_partials != nullptr) {
+    float* prow = p.dq_partials + (int64_t)blockIdx.x * p.R;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const int d = (j * T + tid) * VEC + e;
+        if (d < D && d >= tail0) prow[d - tail0] = dq[j * VEC + e];
+      }
+    }
+  }
+}
+
+// Second stage of the query gradient: column sums of the [rows, R] partials in
+// a fixed order (8 interleaved row groups, then the groups in index order), so
+// the result is bit-identical from call to call.  The reference reduces a
+// [N, R] buffer with ceil(R/32) programs (src/attnres/_kernels/fixed_tail.py:875-899).
+__global__ void __launch_bounds__(256)
+dq_reduce_kernel(const float* __restrict__ partials, int rows, int R,
+                 __nv_bfloat16* __restrict__ dq_bf16, float* __restrict__ dq_f32) {
+  __shared__ float sm[8][33];
+  const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int r = blockIdx.x * 32 + col;
+  float sum = 0.f;
+  if (r < R) {
+    for (int row = grp; row < rows; row += 8) sum += partials[(int64_t)row * R + r];
+  }
+  sm[grp][col] = sum;
+  __syncthreads();
+  if (grp == 0 && r < R) {
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += sm[k][col];
+    if (dq_f32 != nullptr) dq_f32[r] = total;
+    if (dq_bf16 != nullptr) dq_bf16[r] = __float2bfloat16_rn(total);
+  }
+}
+
+}  // namespace attnres_b200

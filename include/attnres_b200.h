@@ -1,0 +1,154 @@
+/*
+ * attnres_b200.h -- C ABI of the B200 (sm_100a) AttnRes read kernels.
+ *
+ * The reference project (jon123boss/fast-attnres) is pure Python + Triton and
+ * has no FFI of its own.  The seam this library plugs into is the pair of
+ * torch.library operators that sit between its public `attnres()` function and
+ * its Triton launches:
+ *
+ *   packed values : attnres::_fixed_tail_forward_with_aux / _fixed_tail_backward
+ *                   (src/attnres/_kernels/fixed_tail.py:904-1034)
+ *   source lists  : attnres::_fixed_tail_sources_forward_with_aux /
+ *                   _fixed_tail_sources_backward
+ *                   (src/attnres/_kernels/fixed_tail_sources.py:78-101, launched by
+ *                   src/attnres/_kernels/fla_full_sources.py:752-894)
+ *
+ * Every entry point below takes plain pointers, sizes and a CUDA stream.  The
+ * library owns no memory: the caller allocates inputs, outputs and the dquery
+ * workspace and keeps them alive until the stream has run the work.  No entry
+ * point synchronises, and every argument error is found on the host before a
+ * kernel is launched.  Calls are re-entrant; calls on different streams may run
+ * concurrently as long as they do not share output or workspace buffers.
+ *
+ * Math (per flattened position n, sources s = 0..S-1, BF16 storage, FP32
+ * arithmetic; validation/oracle.py:5-19):
+ *
+ *   t_s   = v_s[D-R : D]                       the "tail key" of source s
+ *   r_s   = rsqrt(mean(t_s^2) + eps)
+ *   z_s   = scale * r_s * sum(t_s * q)         saved in `logits`
+ *   p     = softmax_s(z)                       (max, 1/sum) saved in `stats`
+ *   out   = bf16(sum_s p_s * v_s)
+ */
+#ifndef ATTNRES_B200_H_
+#define ATTNRES_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATTNRES_B200_ABI_VERSION 1
+/* Envelope of the reference operator (src/attnres/_sources.py:12-13). */
+#define ATTNRES_B200_MAX_SOURCES 129
+#define ATTNRES_B200_MAX_WIDTH 8192
+
+/* Status codes returned by every entry point (0 = success). */
+#define ATTNRES_B200_OK 0
+#define ATTNRES_B200_ERR_NULL_POINTER 1
+#define ATTNRES_B200_ERR_BAD_SOURCE_COUNT 2   /* S outside 1..129 */
+#define ATTNRES_B200_ERR_BAD_WIDTH 3          /* D outside 1..8192 */
+#define ATTNRES_B200_ERR_BAD_RANK 4           /* R outside 1..D */
+#define ATTNRES_B200_ERR_BAD_ROWS 5           /* N < 1 */
+#define ATTNRES_B200_ERR_BAD_SCALAR 6         /* eps <= 0 or non-finite, scale non-finite */
+#define ATTNRES_B200_ERR_MISALIGNED 7         /* a BF16 pointer that is not 2-byte aligned */
+#define ATTNRES_B200_ERR_WORKSPACE 8          /* dquery workspace too small */
+#define ATTNRES_B200_ERR_CUDA 9               /* a CUDA runtime call failed (launch, attribute) */
+#define ATTNRES_B200_ERR_BAD_FLAGS 10
+#define ATTNRES_B200_ERR_NOTHING_TO_DO 11     /* backward with neither value nor query gradient */
+
+/* `flags` bits. */
+#define ATTNRES_B200_FLAG_DEFAULT 0u
+/* Use the layout-generic kernels even when the inputs qualify for the
+ * TMA-staged fast path (used by tests to cover both families). */
+#define ATTNRES_B200_FLAG_FORCE_GENERIC 1u
+
+/* Replaces nothing in the reference; lets a binding check it loaded the
+ * library it was written against. */
+int attnres_b200_abi_version(void);
+
+/* Human-readable text for a status code (static storage, never NULL). */
+const char* attnres_b200_status_string(int status);
+
+/*
+ * Forward read.  Replaces the Triton launches
+ * `_packed_online_forward_kernel` (src/attnres/_kernels/fixed_tail.py:927-958)
+ * and `_fla_standard_forward_kernel`
+ * (src/attnres/_kernels/fla_full_sources.py:776-804).
+ *
+ *   src_ptrs[s]        device address of row 0 of source s (BF16)
+ *   src_row_stride[s]  elements between consecutive rows of source s (may be 0)
+ *   src_feat_stride[s] elements between consecutive features of source s
+ *                      (the three arrays live in HOST memory, length S; a packed
+ *                      [S,N,D] tensor is passed as base + s*stride(0))
+ *   query              device BF16 [R], element stride `query_stride`
+ *   out                device BF16 [N,D], row stride `out_row_stride`, feature stride 1
+ *   logits             device FP32 [S,N] contiguous: scaled logits z_s
+ *   stats              device FP32 [2,N] contiguous: row max, then 1/sum(exp(z-max))
+ *   stream             a cudaStream_t (0 = legacy default stream)
+ */
+int attnres_b200_forward(
+    const void* const* src_ptrs, const int64_t* src_row_stride,
+    const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    void* out, int64_t out_row_stride,
+    float* logits, float* stats,
+    uint32_t flags, void* stream);
+
+/*
+ * Rows the dquery workspace must hold for a backward call of this shape on
+ * `device`: `dq_partials` is FP32 [rows, R].  Pure host function (replaces the
+ * `[N,R]` token partial buffer the reference allocates,
+ * src/attnres/_kernels/fixed_tail.py:981-984).  Returns a negative status on
+ * error.
+ */
+int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t R,
+                                       int32_t device);
+
+/*
+ * Backward read.  Replaces `_packed_online_backward_kernel` +
+ * `_packed_query_reduce_kernel` (src/attnres/_kernels/fixed_tail.py:987-1034)
+ * and `_fla_standard_backward_kernel` + the query reducers
+ * (src/attnres/_kernels/fla_full_sources.py:845-893).
+ *
+ *   grad_out           device BF16 [N,D] with arbitrary row/feature strides
+ *   logits, stats      as written by attnres_b200_forward for the same inputs
+ *   dsrc_ptrs[s]       device BF16 [N,D] gradient of source s, row stride
+ *                      dsrc_row_stride[s], feature stride 1 (host arrays, length S).
+ *                      NULL skips the value gradients.
+ *   dq_partials        device FP32 workspace [dq_partial_rows, R]
+ *   dq_bf16, dq_f32    device [R] outputs, contiguous; either may be NULL.  The
+ *                      FP32 form is the one to all-reduce across GPUs before the
+ *                      BF16 cast.  Both NULL skips the query gradient.
+ *
+ * The query gradient is reduced in a fixed order, so repeated calls are
+ * bit-identical.
+ */
+int attnres_b200_backward(
+    const void* const* src_ptrs, const int64_t* src_row_stride,
+    const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
+    const float* logits, const float* stats,
+    void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
+    float* dq_partials, int32_t dq_partial_rows,
+    void* dq_bf16, float* dq_f32,
+    uint32_t flags, void* stream);
+
+/*
+ * Name of the kernel family the library would pick for a call of this shape
+ * ("tma" or "generic"), for logs and tests.  `aligned` is nonzero when every
+ * pointer is 16-byte aligned, every row stride a multiple of 8 elements and
+ * every feature stride 1.  `backward` selects the backward policy.
+ */
+const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t aligned,
+                                       int32_t backward);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTNRES_B200_H_ */

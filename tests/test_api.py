@@ -1,0 +1,167 @@
+"""Host-side contract of ``attnres`` and ``LearnedQuery`` (no GPU needed).
+
+The cases follow the reference's CPU contract tests (tests/test_api.py:16-61,
+:90-109, :145-156, :224-277 and tests/test_info.py:27-38 of the reference).
+"""
+import importlib.abc
+import inspect
+import sys
+
+import pytest
+import torch
+
+import attnres as package
+from attnres import LearnedQuery, attnres
+from attnres._sources import row_layout
+
+
+def test_public_surface():
+    assert set(package.__all__) == {"attnres", "LearnedQuery", "__version__"}
+    parameters = inspect.signature(attnres).parameters
+    assert list(parameters) == ["values", "query", "eps", "scale"]
+    assert parameters["eps"].default == 2**-23 and parameters["scale"].default == 1.0
+    assert parameters["eps"].kind is inspect.Parameter.KEYWORD_ONLY
+    with pytest.raises(TypeError):
+        attnres(torch.zeros(2, 3, 4, dtype=torch.bfloat16), torch.zeros(4, dtype=torch.bfloat16),
+                keys=torch.zeros(2, 3, 4, dtype=torch.bfloat16))
+
+
+class _RejectTriton(importlib.abc.MetaPathFinder):
+    def find_spec(self, fullname, path=None, target=None):
+        if fullname == "triton" or fullname.startswith("triton."):
+            raise AssertionError(f"attnres attempted to import {fullname}")
+
+
+@pytest.mark.parametrize("container", [list, tuple])
+def test_cpu_source_lists_are_rejected_without_touching_triton(monkeypatch, container):
+    for name in tuple(sys.modules):
+        if name == "triton" or name.startswith("triton."):
+            monkeypatch.delitem(sys.modules, name, raising=False)
+    guard = _RejectTriton()
+    sys.meta_path.insert(0, guard)
+    try:
+        values = container(torch.randn(2, 8, dtype=torch.bfloat16, requires_grad=True)
+                           for _ in range(3))
+        query = torch.randn(4, dtype=torch.bfloat16, requires_grad=True)
+        with pytest.raises(RuntimeError, match="CUDA"):
+            attnres(values, query)
+    finally:
+        sys.meta_path.remove(guard)
+
+
+def test_cpu_packed_and_fp32_inputs_are_rejected():
+    values = torch.randn(5, 2, 13, dtype=torch.bfloat16)
+    query = torch.randn(4, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attnres(values, query)
+    with pytest.raises(TypeError, match="BF16"):
+        attnres(values.float(), query)
+    with pytest.raises(TypeError, match="BF16"):
+        attnres(values, query.float())
+    with pytest.raises(TypeError, match="BF16"):
+        attnres([values[0].float(), values[1].float()], query)
+
+
+def test_scalars_are_validated_before_the_device():
+    values = torch.randn(4, 3, 9, dtype=torch.bfloat16)
+    query = torch.randn(3, dtype=torch.bfloat16)
+    for container in (values, tuple(values.unbind(0))):
+        with pytest.raises(ValueError, match="eps"):
+            attnres(container, query, eps=0.0)
+        with pytest.raises(ValueError, match="eps"):
+            attnres(container, query, eps=float("inf"))
+        with pytest.raises(ValueError, match="scale"):
+            attnres(container, query, scale=float("nan"))
+        with pytest.raises(TypeError, match="eps"):
+            attnres(container, query, eps=True)
+        with pytest.raises(TypeError, match="scale"):
+            attnres(container, query, scale="1")
+        with pytest.raises(TypeError, match="scale"):
+            attnres(container, query, scale=torch.tensor(1.0))
+        with pytest.raises(RuntimeError, match="CUDA"):
+            attnres(container, query, eps=2**-20, scale=0.75)
+
+
+def test_shape_and_container_errors():
+    bf = torch.bfloat16
+    query = torch.zeros(4, dtype=bf)
+    with pytest.raises(TypeError, match="query must be a tensor"):
+        attnres(torch.zeros(2, 3, 8, dtype=bf), [0.0] * 4)
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(8, dtype=bf), query)                      # values rank < 2
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(2, 3, 8, dtype=bf), torch.zeros(2, 2, dtype=bf))  # query rank
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(130, 1, 8, dtype=bf), query)              # S > 129
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(2, 1, 8193, dtype=bf), query)             # D > 8192
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(2, 1, 3, dtype=bf), query)                # R > D
+    with pytest.raises(ValueError):
+        attnres(torch.zeros(2, 0, 8, dtype=bf), query)                # empty axis
+    with pytest.raises(TypeError, match="list/tuple"):
+        attnres({"a": torch.zeros(3, 8, dtype=bf)}, query)
+    with pytest.raises(TypeError, match="only tensors"):
+        attnres([torch.zeros(3, 8, dtype=bf), 1.0], query)
+    with pytest.raises(ValueError, match="1<=S<=129"):
+        attnres([], query)
+    with pytest.raises(ValueError, match="1<=S<=129"):
+        attnres([torch.zeros(1, 8, dtype=bf)] * 130, query)
+    with pytest.raises(ValueError, match="same logical shape"):
+        attnres([torch.zeros(3, 8, dtype=bf), torch.zeros(2, 8, dtype=bf)], query)
+    with pytest.raises(ValueError, match="1<=R<=D"):
+        attnres([torch.zeros(3, 2, dtype=bf)], query)
+    with pytest.raises(ValueError):
+        attnres([torch.zeros((), dtype=bf)], query)                   # source rank < 1
+    with pytest.raises(TypeError, match="dtype/device"):
+        attnres([torch.zeros(3, 8, dtype=bf), torch.zeros(3, 8)], query)
+
+
+def test_learned_query_contract():
+    module = LearnedQuery(16)
+    assert module.query.dtype == torch.bfloat16 and module.query.shape == (16,)
+    assert module().dtype == torch.bfloat16
+    assert 0 < float(module.query.float().std()) < 0.1
+    # Cast to FP32: the parameter is FP32, the query it hands out stays BF16 and
+    # the gradient arrives in FP32.
+    module = LearnedQuery(8).float()
+    out = module()
+    assert out.dtype == torch.bfloat16
+    out.float().sum().backward()
+    assert module.query.grad.dtype == torch.float32
+    with pytest.raises(ValueError):
+        LearnedQuery(0)
+    with pytest.raises(TypeError):
+        LearnedQuery(2.5)
+    with pytest.raises(TypeError):
+        LearnedQuery(True)
+    with pytest.raises(ValueError):
+        LearnedQuery(4, init_std=0.0)
+
+
+def test_row_layout_flattens_affine_batches_and_copies_the_rest():
+    # Same cases as tests/test_row_layout.py:7-41 of the reference.
+    base = torch.arange(2 * 3 * 8, dtype=torch.float32)
+    plain = base.view(2, 3, 8)
+    tensor, row, feat = row_layout(plain)
+    assert tensor is plain and (row, feat) == (8, 1)
+    # singleton axes never constrain the layout
+    single = base[:24].as_strided((3, 1, 8), (8, 16, 1))
+    tensor, row, feat = row_layout(single)
+    assert tensor is single and (row, feat) == (8, 1)
+    # a broadcast row axis has stride 0
+    broadcast = base[:8].expand(5, 8)
+    tensor, row, feat = row_layout(broadcast)
+    assert tensor is broadcast and (row, feat) == (0, 1)
+    # a feature-strided view keeps its stride
+    strided = base.view(6, 8)[:, ::2]
+    tensor, row, feat = row_layout(strided)
+    assert tensor is strided and (row, feat) == (8, 2)
+    # a transposed batch is not affine: it is copied, and only then
+    swapped = plain.transpose(0, 1)
+    tensor, row, feat = row_layout(swapped)
+    assert tensor is not swapped and tensor.is_contiguous() and (row, feat) == (8, 1)
+    assert torch.equal(tensor, swapped)
+    # a single vector
+    tensor, row, feat = row_layout(base[:8])
+    assert (row, feat) == (0, 1)
