@@ -22,6 +22,7 @@ SIGNATURES = {
     "attnres_b200_status_string": (c_char_p, [c_int32]),
     "attnres_b200_kernel_family": (c_char_p, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "attnres_b200_dq_workspace_rows": (c_int32, [c_int64, c_int32, c_int32, c_int32, c_int32]),
+    "attnres_b200_error_flag": (c_int32, [ctypes.POINTER(c_int32), c_int32]),
     "attnres_b200_forward": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
         c_int32, c_int64, c_int32, c_int32,
@@ -109,6 +110,13 @@ def backward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_s
         None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
         partials_ptr, partial_rows, dq_bf16_ptr, dq_f32_ptr, flags, stream)
     check(status, "attnres_b200_backward")
+
+
+def error_flag(clear: bool = False) -> int:
+    """The sticky "a kernel gave up waiting" flag of the current device (synchronises)."""
+    value = c_int32(0)
+    check(load().attnres_b200_error_flag(ctypes.byref(value), int(clear)), "attnres_b200_error_flag")
+    return int(value.value)
 
 
 def kernel_family(S, D, R, aligned, backward_pass) -> str:

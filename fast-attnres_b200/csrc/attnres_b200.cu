@@ -7,7 +7,8 @@
 
 #include "common.cuh"
 #include "generic_kernels.cuh"
-#include "tma_kernels.cuh"
+#include "fwd_ring_kernel.cuh"
+#include "bwd_stash_kernel.cuh"
 
 namespace attnres_b200 {
 namespace {
@@ -150,6 +151,24 @@ extern "C" const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t 
   return tma_fwd_supported(S, D, R) ? "tma" : "generic";
 }
 
+extern "C" int attnres_b200_error_flag(int32_t* flag, int32_t clear) {
+  if (flag == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  int value = 0;
+  if (cudaMemcpyFromSymbol(&value, g_error_flag, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return ATTNRES_B200_ERR_CUDA;
+  }
+  *flag = value;
+  if (clear && value != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_error_flag, &zero, sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      return ATTNRES_B200_ERR_CUDA;
+    }
+  }
+  return ATTNRES_B200_OK;
+}
+
 extern "C" int attnres_b200_forward(
     const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
     int32_t S, int64_t N, int32_t D, int32_t R,
@@ -260,7 +279,7 @@ extern "C" int attnres_b200_backward(
   p.stats = stats;
   p.dq_partials = want_dq ? dq_partials : nullptr;
   vec = vec && D % 8 == 0 && aligned16(grad_out) && go_feat_stride == 1 &&
-        (N == 1 || go_row_stride % 8 == 0);
+        (N == 1 || go_row_stride % 8 == 0) && (!want_dq || aligned16(dq_partials));
 
   int device = 0, sms = 0;
   if (int st = current_device(&device)) return st;

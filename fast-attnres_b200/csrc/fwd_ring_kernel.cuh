@@ -1,0 +1,325 @@
+// TMA-staged forward of the AttnRes read for the aligned layout (feature stride 1,
+// 16-byte aligned rows, D and D-R multiples of 8).
+//
+// A position is owned by a GROUP of G warps (G = 1 for D <= 1024, 2 for 2048,
+// 4 for 4096, 8 for 8192); every lane owns four 16-byte chunks of the row, so
+// the FP32 accumulator, the query lanes and the current batch all stay in
+// registers.  Each group streams its (position, source) rows through its own
+// ring of shared-memory stages filled by 1-D bulk asynchronous copies
+// (cp.async.bulk + mbarrier complete_tx).  The ring refills itself: as soon as
+// the group has moved a batch of two source rows into registers, its leader
+// lane issues the copies for the items that will reuse those stages, so a group
+// always has `stages` rows in flight without a producer warp or "empty"
+// barriers.  Per batch the lanes reduce (sum of squares, dot with the query) of
+// both sources with one folded butterfly, the warps of a group meet at a named
+// barrier, and every lane folds the batch into its accumulator with an online
+// softmax.  Arithmetic on the row uses the packed FP32x2 FMA of sm_100.
+#pragma once
+
+#include "tma_common.cuh"
+
+namespace attnres_b200 {
+
+constexpr int kRingChunks = 4;  // 16-byte chunks per lane
+constexpr int kRingBatch = 2;   // sources folded per reduction
+constexpr int kRingMaxGroupWarps = 8;
+
+struct FwdRingPlan {
+  int group_warps;  // G
+  int cta_warps;    // 4 or 8
+  int stages;       // ring depth per group
+  int ctas_per_sm;
+  uint32_t off_bars;
+  uint32_t off_part;
+  uint32_t off_abort;
+  uint32_t smem_bytes;
+};
+
+inline bool make_fwd_plan(int S, int D, int R, FwdRingPlan* plan) {
+  (void)S;
+  if (!tma_shape_ok(D, R)) return false;
+  const int chunks = D / 8;
+  int need = (chunks + 32 * kRingChunks - 1) / (32 * kRingChunks);
+  int G = 1;
+  while (G < need) G <<= 1;
+  if (G > kRingMaxGroupWarps) return false;
+  FwdRingPlan p;
+  p.group_warps = G;
+  p.cta_warps = G > 4 ? 8 : 4;
+  p.ctas_per_sm = p.cta_warps == 4 ? 3 : 1;
+  const int groups = p.cta_warps / G;
+  const uint32_t row_bytes = (uint32_t)D * 2u;
+  const uint32_t fixed = 4u * 8u * 8u + 4u * 2u * 2u * kRingBatch * kRingMaxGroupWarps * 4u + 16u + 1024u;
+  const uint32_t budget = (uint32_t)kSmemPerSm / (uint32_t)p.ctas_per_sm;
+  int stages = (int)((budget - fixed) / ((uint32_t)groups * row_bytes));
+  if (stages > 8) stages = 8;
+  if (stages < 4) return false;
+  p.stages = stages;
+  uint32_t off = (uint32_t)groups * (uint32_t)stages * row_bytes;
+  p.off_bars = align_up(off, 8);
+  off = p.off_bars + (uint32_t)groups * (uint32_t)stages * 8u;
+  p.off_part = align_up(off, 16);
+  off = p.off_part + (uint32_t)groups * 2u * 2u * kRingBatch * kRingMaxGroupWarps * 4u;
+  p.off_abort = off;
+  off += 16;
+  p.smem_bytes = off;
+  if (p.smem_bytes > (uint32_t)kSmemPerCtaMax) return false;
+  *plan = p;
+  return true;
+}
+
+inline bool tma_fwd_supported(int S, int D, int R) {
+  FwdRingPlan plan;
+  return make_fwd_plan(S, D, R, &plan);
+}
+
+__device__ __forceinline__ void group_sync(int group, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 1)
+fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ FwdRingPlan plan) {
+  constexpr int NV = kRingChunks, B = kRingBatch;
+  static_assert(B == 2, "the folded reduction below is written for two sources per batch");
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = plan.group_warps, groups = WARPS / G;
+  const int group = warp / G, wig = warp - group * G;
+  const int L = G * 32, gl = wig * 32 + lane;
+  const int S = p.S, D = p.D, R = p.R;
+  const int CH = D / 8, c0 = (D - R) / 8, nst = plan.stages;
+  const uint32_t row_bytes = (uint32_t)D * 2u;
+  unsigned char* ring = smem + (size_t)group * (size_t)nst * row_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + plan.off_bars) + group * nst;
+  float* part_sm = reinterpret_cast<float*>(smem + plan.off_part) +
+                   group * (2 * 2 * B * kRingMaxGroupWarps);  // [2][2B][8]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + plan.off_abort);
+
+  if (tid == 0) {
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + plan.off_bars);
+    for (int i = 0; i < groups * nst; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // The lane's chunks and its query lanes (zero outside the tail key).
+  bool in_row[NV], in_tail[NV];
+  float2 q2[NV][4];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = gl + j * L;
+    in_row[j] = c < CH;
+    in_tail[j] = in_row[j] && c >= c0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float lo = 0.f, hi = 0.f;
+      if (in_tail[j]) {
+        const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
+        lo = __bfloat162float(p.query[r * p.query_stride]);
+        hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
+      }
+      q2[j][k] = make_float2(lo, hi);
+    }
+  }
+
+  const int64_t total_groups = (int64_t)gridDim.x * groups;
+  const int64_t gid = (int64_t)blockIdx.x * groups + group;
+  const int64_t my_rows = gid < p.N ? (p.N - gid + total_groups - 1) / total_groups : 0;
+  const uint64_t total_items = (uint64_t)my_rows * (uint64_t)S;
+  const bool leader = gl == 0;
+
+  // Leader's issue cursor: items are (row, source) pairs in consumption order.
+  uint64_t issued = 0;
+  int64_t issue_row = gid;
+  int issue_s = 0;
+  auto issue_one = [&]() {
+    const uint32_t stage = (uint32_t)(issued % (uint64_t)nst);
+    mbar_expect_tx(&full_bar[stage], row_bytes);
+    bulk_load(ring + (size_t)stage * row_bytes,
+              p.src.ptr[issue_s] + issue_row * p.src.row_stride[issue_s], row_bytes,
+              &full_bar[stage]);
+    ++issued;
+    if (++issue_s == S) {
+      issue_s = 0;
+      issue_row += total_groups;
+    }
+  };
+  if (leader) {
+    while (issued < total_items && issued < (uint64_t)nst) issue_one();
+  }
+
+  uint64_t consumed = 0;
+  int buf = 0;
+  const float rank_f = (float)R;
+  for (int64_t row = gid; row < p.N; row += total_groups) {
+    float2 acc[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[j][k] = make_float2(0.f, 0.f);
+    float run_max = -INFINITY, run_sum = 0.f;
+
+    for (int s0 = 0; s0 < S; s0 += B, buf ^= 1) {
+      const int nb = (S - s0) < B ? (S - s0) : B;
+      float2 v2[B][NV][4];
+      float part[2 * B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        float2 ss2 = make_float2(0.f, 0.f), dt2 = make_float2(0.f, 0.f);
+        if (b < nb) {
+          const uint64_t it = consumed + b;
+          const uint32_t stage = (uint32_t)(it % (uint64_t)nst);
+          mbar_wait(&full_bar[stage], (uint32_t)((it / (uint64_t)nst) & 1u), abort_flag);
+          const uint4* vrow = reinterpret_cast<const uint4*>(ring + (size_t)stage * row_bytes);
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            if (in_row[j]) {
+              const uint4 raw = vrow[gl + j * L];
+              v2[b][j][0] = make_float2(bf16x2_lo(raw.x), bf16x2_hi(raw.x));
+              v2[b][j][1] = make_float2(bf16x2_lo(raw.y), bf16x2_hi(raw.y));
+              v2[b][j][2] = make_float2(bf16x2_lo(raw.z), bf16x2_hi(raw.z));
+              v2[b][j][3] = make_float2(bf16x2_lo(raw.w), bf16x2_hi(raw.w));
+              if (in_tail[j]) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  ss2 = __ffma2_rn(v2[b][j][k], v2[b][j][k], ss2);
+                  dt2 = __ffma2_rn(v2[b][j][k], q2[j][k], dt2);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) v2[b][j][k] = make_float2(0.f, 0.f);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < NV; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v2[b][j][k] = make_float2(0.f, 0.f);
+        }
+        part[2 * b] = ss2.x + ss2.y;
+        part[2 * b + 1] = dt2.x + dt2.y;
+      }
+
+      // Folded butterfly over the warp: four values cost 3 + 3 shuffles.  Afterwards
+      // lane 0 / 8 / 16 / 24 (and their neighbours) hold the warp total of value 0 / 1 / 2 / 3.
+      const bool up16 = (lane & 16) != 0;
+      float keep0 = up16 ? part[2] : part[0];
+      float keep1 = up16 ? part[3] : part[1];
+      keep0 += __shfl_xor_sync(0xffffffffu, up16 ? part[0] : part[2], 16);
+      keep1 += __shfl_xor_sync(0xffffffffu, up16 ? part[1] : part[3], 16);
+      const bool up8 = (lane & 8) != 0;
+      float keep = up8 ? keep1 : keep0;
+      keep += __shfl_xor_sync(0xffffffffu, up8 ? keep0 : keep1, 8);
+      keep += __shfl_xor_sync(0xffffffffu, keep, 4);
+      keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+      keep += __shfl_xor_sync(0xffffffffu, keep, 1);
+      float tot[2 * B];
+      if (G == 1) {
+#pragma unroll
+        for (int i = 0; i < 2 * B; ++i) tot[i] = __shfl_sync(0xffffffffu, keep, i * 8);
+      } else {
+        float* mine = part_sm + buf * (2 * B * kRingMaxGroupWarps);
+        if ((lane & 7) == 0) mine[(lane >> 3) * kRingMaxGroupWarps + wig] = keep;
+        group_sync(group, L);
+#pragma unroll
+        for (int i = 0; i < 2 * B; ++i) {
+          float t = 0.f;
+          for (int w = 0; w < G; ++w) t += mine[i * kRingMaxGroupWarps + w];
+          tot[i] = t;
+        }
+      }
+      // Every lane of the group has read its chunks of these stages: refill them.
+      if (leader) {
+        fence_proxy_async();
+        while (issued < total_items && issued < consumed + (uint64_t)nb + (uint64_t)nst) issue_one();
+      }
+
+      // Online softmax over the batch.
+      float z[B];
+      float new_max = run_max;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        z[b] = -INFINITY;
+        if (b < nb) {
+          const float inv_rms = rsqrtf(tot[2 * b] / rank_f + p.eps);
+          z[b] = tot[2 * b + 1] * inv_rms * p.scale;
+          new_max = fmaxf(new_max, z[b]);
+        }
+      }
+      if (new_max != run_max) {
+        const float rescale = __expf(run_max - new_max);
+        run_sum *= rescale;
+        const float2 r2 = make_float2(rescale, rescale);
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[j][k] = __fmul2_rn(acc[j][k], r2);
+        run_max = new_max;
+      }
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (b < nb) {
+          const float w = __expf(z[b] - new_max);
+          run_sum += w;
+          const float2 w2 = make_float2(w, w);
+#pragma unroll
+          for (int j = 0; j < NV; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[j][k] = __ffma2_rn(w2, v2[b][j][k], acc[j][k]);
+          if (leader) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
+        }
+      }
+      consumed += (uint64_t)nb;
+    }
+
+    const float inv_sum = 1.0f / run_sum;
+    if (leader) {
+      p.stats[row] = run_max;
+      p.stats[p.N + row] = inv_sum;
+    }
+    __nv_bfloat16* orow = p.out + row * p.out_row_stride;
+    const float2 i2 = make_float2(inv_sum, inv_sum);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (in_row[j]) {
+        uint4 packed;
+        float2 o;
+        o = __fmul2_rn(acc[j][0], i2);
+        packed.x = pack_bf16x2(o.x, o.y);
+        o = __fmul2_rn(acc[j][1], i2);
+        packed.y = pack_bf16x2(o.x, o.y);
+        o = __fmul2_rn(acc[j][2], i2);
+        packed.z = pack_bf16x2(o.x, o.y);
+        o = __fmul2_rn(acc[j][3], i2);
+        packed.w = pack_bf16x2(o.x, o.y);
+        *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = packed;
+      }
+    }
+  }
+}
+
+inline int launch_fwd_tma(const FwdParams& p, int sms, cudaStream_t stream) {
+  FwdRingPlan plan;
+  if (!make_fwd_plan(p.S, p.D, p.R, &plan)) return 9;
+  const int groups = plan.cta_warps / plan.group_warps;
+  const int64_t wanted = (p.N + groups - 1) / groups;
+  const int64_t cap = (int64_t)sms * plan.ctas_per_sm;
+  const int grid = (int)(wanted < cap ? wanted : cap);
+  if (plan.cta_warps == 4) {
+    if (int st = prepare_kernel(fwd_ring_kernel<4>, plan.smem_bytes)) return st;
+    fwd_ring_kernel<4><<<grid, 128, plan.smem_bytes, stream>>>(p, plan);
+  } else {
+    if (int st = prepare_kernel(fwd_ring_kernel<8>, plan.smem_bytes)) return st;
+    fwd_ring_kernel<8><<<grid, 256, plan.smem_bytes, stream>>>(p, plan);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 9;
+}
+
+}  // namespace attnres_b200

@@ -148,6 +148,16 @@ int attnres_b200_backward(
 const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t aligned,
                                        int32_t backward);
 
+/*
+ * Diagnostics (no counterpart in the reference).  The TMA-staged kernels bound
+ * every wait on a shared-memory barrier; a CTA that gives up sets a sticky
+ * device-side flag and finishes with meaningless results instead of hanging.
+ * This call copies the flag of the current device to `*flag` (0 = no kernel ever
+ * gave up) and optionally clears it.  It SYNCHRONISES the device: use it in
+ * tests and after failures, not on the hot path.
+ */
+int attnres_b200_error_flag(int32_t* flag, int32_t clear);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,8 +59,13 @@ def oracle_with_grads(values, query, upstream, *, eps: float = 2**-23, scale: fl
 
 
 def closed_form(values: np.ndarray, query: np.ndarray, upstream: np.ndarray | None = None, *,
-                eps: float = 2**-23, scale: float = 1.0):
+                eps: float = 2**-23, scale: float = 1.0, logits: np.ndarray | None = None):
     """Float64 forward (and backward when ``upstream`` is given) on ``[S, N, D]`` arrays.
+
+    ``logits`` (``[S, N]``) replaces the computed logits z when given.  Where one FP32
+    ulp of a logit is not small against 1 (|z| > 1e6), two correct FP32 evaluations of z
+    give visibly different softmax weights; passing a kernel's own saved logits checks
+    everything downstream of them exactly.
 
     Returns ``out`` or ``(out, dV, dq)``, all float64 and un-rounded:
 
@@ -76,7 +81,7 @@ def closed_form(values: np.ndarray, query: np.ndarray, upstream: np.ndarray | No
     tail = v[..., -rank:]
     r = 1.0 / np.sqrt((tail * tail).mean(-1) + eps)             # [S, N]
     k = tail * r[..., None]
-    z = scale * (k * q).sum(-1)
+    z = scale * (k * q).sum(-1) if logits is None else np.asarray(logits, dtype=np.float64)
     z_shift = z - z.max(0, keepdims=True)
     p = np.exp(z_shift)
     p /= p.sum(0, keepdims=True)

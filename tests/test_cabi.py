@@ -91,7 +91,14 @@ def test_workspace_rows_validates_shape():
     assert lib.attnres_b200_dq_workspace_rows(4, 2, 16, 17, 0) == -4
 
 
-def test_kernel_family_names():
+def test_kernel_family_selection_is_a_pure_host_decision():
+    from attnres import _native
+    assert _native.kernel_family(9, 2048, 2048, True, False) == "tma"
+    assert _native.kernel_family(9, 2048, 2048, True, True) == "tma"
+    assert _native.kernel_family(16, 4096, 1024, True, True) == "tma"
+    assert _native.kernel_family(9, 2048, 2048, False, True) == "generic"
+    assert _native.kernel_family(9, 3000, 127, True, False) == "generic"
+    assert _native.kernel_family(49, 4096, 4096, True, True) == "generic"   # row exceeds shared memory
+    assert _native.kernel_family(49, 4096, 4096, True, False) == "tma"
     assert _native.kernel_family(2, 1024, 1024, False, False) == "generic"
-    assert _native.kernel_family(2, 1024, 1024, True, False) in ("tma", "generic")
     assert _native.kernel_family(0, 1024, 1024, True, False) == "invalid"
