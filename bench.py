@@ -326,7 +326,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     value = tokens_per_step / (ms_per_step * 1e-3)
 
     # ---- end to end: pinned host buffers -> public API -> host results
-    e2e = run_e2e(args, cells, device, distributed)
+    e2e = (run_e2e(args, cells, device, distributed) if not args.skip_e2e
+           else {"ms_per_step": float("nan"), "h2d": 0, "d2h": 0, "steps": 0})
     if distributed:
         worst = torch.tensor([e2e["ms_per_step"]], device=device, dtype=torch.float64)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
@@ -352,7 +353,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "gbs": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9, 1),
             "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
         })
-    cpu_rate, cpu_seconds, threads = cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS)
+    cpu_rate, cpu_seconds, threads = (cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS) if not args.skip_cpu
+                                      else (float("nan"), 0.0, 0))
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -439,13 +441,85 @@ def run_e2e(args, cells, device, distributed) -> dict:
     return {"ms_per_step": start.elapsed_time(stop) / steps, "h2d": h2d, "d2h": d2h, "steps": steps}
 
 
+def run_single_cell(args) -> None:
+    """`--cell S,D[,R]`: one shape, eager launches through the C ABI, per-call CUDA-event
+    times.  This is the small case the ncu captures under profiles/ were taken on."""
+    from attnres import _native
+    parts = [int(x) for x in args.cell.split(",")]
+    sources, width = parts[0], parts[1]
+    rank = parts[2] if len(parts) > 2 else width
+    rows = args.rows
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    generator = torch.Generator(device=device).manual_seed(SEED)
+    values = torch.randn(sources, rows, width, device=device, dtype=torch.bfloat16, generator=generator)
+    query = (torch.randn(rank, device=device, generator=generator) * 0.02).to(torch.bfloat16)
+    upstream = torch.randn(rows, width, device=device, dtype=torch.bfloat16, generator=generator)
+    out = torch.empty(rows, width, device=device, dtype=torch.bfloat16)
+    grad = torch.empty_like(values)
+    logits = torch.empty(sources, rows, device=device, dtype=torch.float32)
+    stats = torch.empty(2, rows, device=device, dtype=torch.float32)
+    partial_rows = _native.dq_workspace_rows(rows, sources, width, rank, 0)
+    partials = torch.empty(partial_rows, rank, device=device, dtype=torch.float32)
+    dq = torch.empty(rank, device=device, dtype=torch.bfloat16)
+    flush = torch.empty(256 * 1024 * 1024, device=device, dtype=torch.uint8)
+    step = rows * width * 2
+    src = [values.data_ptr() + s * step for s in range(sources)]
+    dst = [grad.data_ptr() + s * step for s in range(sources)]
+    stream = torch.cuda.current_stream().cuda_stream
+    scale = rank ** -0.5 if rank != width else 1.0
+    flags = _native.FLAG_FORCE_GENERIC if args.generic else 0
+    fwd_ms, bwd_ms = [], []
+    for index in range(args.warmup + args.steps):
+        flush.zero_()  # 256 MB write: evicts the 126 MB L2 between timed launches
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        _native.forward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
+                        query.data_ptr(), 1, 2**-23, scale, out.data_ptr(), width,
+                        logits.data_ptr(), stats.data_ptr(), flags, stream)
+        e1.record()
+        flush.zero_()
+        e1b = torch.cuda.Event(enable_timing=True)
+        e1b.record()
+        _native.backward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
+                         query.data_ptr(), 1, 2**-23, scale, upstream.data_ptr(), width, 1,
+                         logits.data_ptr(), stats.data_ptr(), dst, [width] * sources,
+                         partials.data_ptr(), partial_rows, dq.data_ptr(), None, flags, stream)
+        e2.record()
+        torch.cuda.synchronize()
+        if index >= args.warmup:
+            fwd_ms.append(e0.elapsed_time(e1))
+            bwd_ms.append(e1b.elapsed_time(e2))
+    fwd_bytes = rows * (2 * sources * width + 2 * width)
+    bwd_bytes = rows * (4 * sources * width + 2 * width)
+    peak, _ = measured_peak_gbs()
+    f, b = sorted(fwd_ms)[len(fwd_ms) // 2], sorted(bwd_ms)[len(bwd_ms) // 2]
+    print(json.dumps({"cell": [sources, rows, width, rank], "fwd_ms": f, "bwd_ms": b,
+                      "fwd_gbs": fwd_bytes / f / 1e6, "bwd_gbs": bwd_bytes / b / 1e6,
+                      "fwd_frac": fwd_bytes / f / 1e6 / peak, "bwd_frac": bwd_bytes / b / 1e6 / peak,
+                      "family_fwd": _native.kernel_family(sources, width, rank, True, False)
+                      if not args.generic else "generic",
+                      "family_bwd": _native.kernel_family(sources, width, rank, True, True)
+                      if not args.generic else "generic"}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--skip-e2e", action="store_true",
+                        help="profiling runs: leave out the host-buffer end-to-end leg")
+    parser.add_argument("--skip-cpu", action="store_true",
+                        help="profiling runs: leave out the CPU-oracle leg")
+    parser.add_argument("--cell", default=None, help="S,D[,R]: time one shape instead of the sweep")
+    parser.add_argument("--rows", type=int, default=ROWS, help="rows of the --cell run")
+    parser.add_argument("--generic", action="store_true", help="--cell: force the generic kernels")
     args = parser.parse_args()
+    if args.cell is not None:
+        run_single_cell(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -134,29 +134,33 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   const uint64_t total_items = (uint64_t)my_rows * (uint64_t)S;
   const bool leader = gl == 0;
 
-  // Leader's issue cursor: items are (row, source) pairs in consumption order.
-  uint64_t issued = 0;
+  // Leader's issue cursor: items are (row, source) pairs in consumption order.  Stage
+  // indices and phase bits advance incrementally (no division on the hot path).
+  uint64_t to_issue = total_items;  // items not yet requested
+  int in_flight = 0;                // requested, not yet consumed
+  uint32_t issue_stage = 0;
   int64_t issue_row = gid;
   int issue_s = 0;
   auto issue_one = [&]() {
-    const uint32_t stage = (uint32_t)(issued % (uint64_t)nst);
-    mbar_expect_tx(&full_bar[stage], row_bytes);
-    bulk_load(ring + (size_t)stage * row_bytes,
+    mbar_expect_tx(&full_bar[issue_stage], row_bytes);
+    bulk_load(ring + (size_t)issue_stage * row_bytes,
               p.src.ptr[issue_s] + issue_row * p.src.row_stride[issue_s], row_bytes,
-              &full_bar[stage]);
-    ++issued;
+              &full_bar[issue_stage]);
+    --to_issue;
+    ++in_flight;
+    if (++issue_stage == (uint32_t)nst) issue_stage = 0;
     if (++issue_s == S) {
       issue_s = 0;
       issue_row += total_groups;
     }
   };
   if (leader) {
-    while (issued < total_items && issued < (uint64_t)nst) issue_one();
+    while (to_issue > 0 && in_flight < nst) issue_one();
   }
 
-  uint64_t consumed = 0;
+  uint32_t use_stage = 0, use_phase = 0;  // stage and phase bit of the next item to consume
   int buf = 0;
-  const float rank_f = (float)R;
+  const float inv_rank = 1.0f / (float)R;
   for (int64_t row = gid; row < p.N; row += total_groups) {
     float2 acc[NV][4];
 #pragma unroll
@@ -173,9 +177,12 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       for (int b = 0; b < B; ++b) {
         float2 ss2 = make_float2(0.f, 0.f), dt2 = make_float2(0.f, 0.f);
         if (b < nb) {
-          const uint64_t it = consumed + b;
-          const uint32_t stage = (uint32_t)(it % (uint64_t)nst);
-          mbar_wait(&full_bar[stage], (uint32_t)((it / (uint64_t)nst) & 1u), abort_flag);
+          uint32_t stage = use_stage + b, phase = use_phase;
+          if (stage >= (uint32_t)nst) {
+            stage -= (uint32_t)nst;
+            phase ^= 1u;
+          }
+          mbar_wait(&full_bar[stage], phase, abort_flag);
           const uint4* vrow = reinterpret_cast<const uint4*>(ring + (size_t)stage * row_bytes);
 #pragma unroll
           for (int j = 0; j < NV; ++j) {
@@ -238,7 +245,8 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       // Every lane of the group has read its chunks of these stages: refill them.
       if (leader) {
         fence_proxy_async();
-        while (issued < total_items && issued < consumed + (uint64_t)nb + (uint64_t)nst) issue_one();
+        in_flight -= nb;
+        while (to_issue > 0 && in_flight < nst) issue_one();
       }
 
       // Online softmax over the batch.
@@ -248,7 +256,7 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       for (int b = 0; b < B; ++b) {
         z[b] = -INFINITY;
         if (b < nb) {
-          const float inv_rms = rsqrtf(tot[2 * b] / rank_f + p.eps);
+          const float inv_rms = rsqrtf(tot[2 * b] * inv_rank + p.eps);
           z[b] = tot[2 * b + 1] * inv_rms * p.scale;
           new_max = fmaxf(new_max, z[b]);
         }
@@ -276,7 +284,11 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
           if (leader) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
         }
       }
-      consumed += (uint64_t)nb;
+      use_stage += (uint32_t)nb;
+      if (use_stage >= (uint32_t)nst) {
+        use_stage -= (uint32_t)nst;
+        use_phase ^= 1u;
+      }
     }
 
     const float inv_sum = 1.0f / run_sum;
@@ -301,6 +313,13 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
         packed.w = pack_bf16x2(o.x, o.y);
         *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = packed;
       }
+    }
+  }
+  // Normal exit: every copy issued was waited for.  After an aborted wait some may still
+  // be in flight: hold the CTA (and so its shared memory) for 200 us before retiring.
+  if (*abort_flag) {
+    const uint64_t start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ull) {
     }
   }
 }
