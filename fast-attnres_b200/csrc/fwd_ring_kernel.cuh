@@ -14,6 +14,12 @@
 // both sources with one folded butterfly, the warps of a group meet at a named
 // barrier, and every lane folds the batch into its accumulator with an online
 // softmax.  Arithmetic on the row uses the packed FP32x2 FMA of sm_100.
+//
+// The kernel is specialised at compile time on G and on TAIL0, the first of the
+// lane's four chunks that lies in the tail key when the boundary D-R falls on a
+// multiple of the group width (TAIL0 = 0 is R = D; D = 4096 with R = 1024 is
+// TAIL0 = 3), so the common shapes run without per-chunk predicates.  TAIL0 = -1
+// is the predicated form for every other aligned shape.
 #pragma once
 
 #include "tma_common.cuh"
@@ -29,6 +35,7 @@ struct FwdRingPlan {
   int cta_warps;    // 4 or 8
   int stages;       // ring depth per group
   int ctas_per_sm;
+  int tail0;        // compile-time tail boundary in chunks-per-lane, or -1
   uint32_t off_bars;
   uint32_t off_part;
   uint32_t off_abort;
@@ -47,6 +54,8 @@ inline bool make_fwd_plan(int S, int D, int R, FwdRingPlan* plan) {
   p.group_warps = G;
   p.cta_warps = G > 4 ? 8 : 4;
   p.ctas_per_sm = p.cta_warps == 4 ? 3 : 1;
+  const int lanes = 32 * G, c0 = (D - R) / 8;
+  p.tail0 = (chunks == lanes * kRingChunks && c0 % lanes == 0) ? c0 / lanes : -1;
   const int groups = p.cta_warps / G;
   const uint32_t row_bytes = (uint32_t)D * 2u;
   const uint32_t fixed = 4u * 8u * 8u + 4u * 2u * 2u * kRingBatch * kRingMaxGroupWarps * 4u + 16u + 1024u;
@@ -81,28 +90,41 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 1)
+// Wait with the polling loop kept out of line: the common case is one try_wait.
+__device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  mbar_wait(bar, parity, abort_flag);
+}
+
+__device__ __forceinline__ void mbar_wait_fast(uint64_t* bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  if (!mbar_try_wait(bar, parity)) mbar_wait_slow(bar, parity, abort_flag);
+}
+
+template <int G, int TAIL0>
+__global__ void __launch_bounds__((G > 4 ? 8 : 4) * 32, G > 4 ? 1 : 3)
 fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ FwdRingPlan plan) {
   constexpr int NV = kRingChunks, B = kRingBatch;
+  constexpr int WARPS = G > 4 ? 8 : 4;
+  constexpr int GROUPS = WARPS / G;
+  constexpr int L = G * 32;
+  constexpr bool STATIC_TAIL = TAIL0 >= 0;
   static_assert(B == 2, "the folded reduction below is written for two sources per batch");
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = plan.group_warps, groups = WARPS / G;
-  const int group = warp / G, wig = warp - group * G;
-  const int L = G * 32, gl = wig * 32 + lane;
+  const int group = warp / G, wig = warp % G;
+  const int gl = wig * 32 + lane;
   const int S = p.S, D = p.D, R = p.R;
   const int CH = D / 8, c0 = (D - R) / 8, nst = plan.stages;
   const uint32_t row_bytes = (uint32_t)D * 2u;
   unsigned char* ring = smem + (size_t)group * (size_t)nst * row_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + plan.off_bars) + group * nst;
-  float* part_sm = reinterpret_cast<float*>(smem + plan.off_part) +
-                   group * (2 * 2 * B * kRingMaxGroupWarps);  // [2][2B][8]
+  float4* part_sm = reinterpret_cast<float4*>(smem + plan.off_part) +
+                    group * (2 * kRingMaxGroupWarps);  // [2][8] x (ss0, dt0, ss1, dt1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + plan.off_abort);
 
   if (tid == 0) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + plan.off_bars);
-    for (int i = 0; i < groups * nst; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < GROUPS * nst; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -114,8 +136,8 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int c = gl + j * L;
-    in_row[j] = c < CH;
-    in_tail[j] = in_row[j] && c >= c0;
+    in_row[j] = STATIC_TAIL ? true : c < CH;
+    in_tail[j] = STATIC_TAIL ? (j >= TAIL0) : (c < CH && c >= c0);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo = 0.f, hi = 0.f;
@@ -128,37 +150,37 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     }
   }
 
-  const int64_t total_groups = (int64_t)gridDim.x * groups;
-  const int64_t gid = (int64_t)blockIdx.x * groups + group;
+  const int64_t total_groups = (int64_t)gridDim.x * GROUPS;
+  const int64_t gid = (int64_t)blockIdx.x * GROUPS + group;
   const int64_t my_rows = gid < p.N ? (p.N - gid + total_groups - 1) / total_groups : 0;
-  const uint64_t total_items = (uint64_t)my_rows * (uint64_t)S;
   const bool leader = gl == 0;
 
   // Leader's issue cursor: items are (row, source) pairs in consumption order.  Stage
   // indices and phase bits advance incrementally (no division on the hot path).
-  uint64_t to_issue = total_items;  // items not yet requested
+  int64_t rows_to_issue = my_rows;  // rows with at least one source not yet requested
   int in_flight = 0;                // requested, not yet consumed
-  uint32_t issue_stage = 0;
+  int issue_stage = 0;
   int64_t issue_row = gid;
   int issue_s = 0;
   auto issue_one = [&]() {
     mbar_expect_tx(&full_bar[issue_stage], row_bytes);
-    bulk_load(ring + (size_t)issue_stage * row_bytes,
+    bulk_load(ring + (uint32_t)issue_stage * row_bytes,
               p.src.ptr[issue_s] + issue_row * p.src.row_stride[issue_s], row_bytes,
               &full_bar[issue_stage]);
-    --to_issue;
     ++in_flight;
-    if (++issue_stage == (uint32_t)nst) issue_stage = 0;
+    if (++issue_stage == nst) issue_stage = 0;
     if (++issue_s == S) {
       issue_s = 0;
       issue_row += total_groups;
+      --rows_to_issue;
     }
   };
   if (leader) {
-    while (to_issue > 0 && in_flight < nst) issue_one();
+    while (rows_to_issue > 0 && in_flight < nst) issue_one();
   }
 
-  uint32_t use_stage = 0, use_phase = 0;  // stage and phase bit of the next item to consume
+  int use_stage = 0;
+  uint32_t use_phase = 0;  // stage and phase bit of the next item to consume
   int buf = 0;
   const float inv_rank = 1.0f / (float)R;
   for (int64_t row = gid; row < p.N; row += total_groups) {
@@ -177,31 +199,32 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       for (int b = 0; b < B; ++b) {
         float2 ss2 = make_float2(0.f, 0.f), dt2 = make_float2(0.f, 0.f);
         if (b < nb) {
-          uint32_t stage = use_stage + b, phase = use_phase;
-          if (stage >= (uint32_t)nst) {
-            stage -= (uint32_t)nst;
+          int stage = use_stage + b;
+          uint32_t phase = use_phase;
+          if (stage >= nst) {
+            stage -= nst;
             phase ^= 1u;
           }
-          mbar_wait(&full_bar[stage], phase, abort_flag);
-          const uint4* vrow = reinterpret_cast<const uint4*>(ring + (size_t)stage * row_bytes);
+          mbar_wait_fast(&full_bar[stage], phase, abort_flag);
+          const uint4* vrow = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
+          uint4 raw[NV];
 #pragma unroll
           for (int j = 0; j < NV; ++j) {
-            if (in_row[j]) {
-              const uint4 raw = vrow[gl + j * L];
-              v2[b][j][0] = make_float2(bf16x2_lo(raw.x), bf16x2_hi(raw.x));
-              v2[b][j][1] = make_float2(bf16x2_lo(raw.y), bf16x2_hi(raw.y));
-              v2[b][j][2] = make_float2(bf16x2_lo(raw.z), bf16x2_hi(raw.z));
-              v2[b][j][3] = make_float2(bf16x2_lo(raw.w), bf16x2_hi(raw.w));
-              if (in_tail[j]) {
+            if (in_row[j]) raw[j] = vrow[j * L];
+            else raw[j] = make_uint4(0u, 0u, 0u, 0u);
+          }
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  ss2 = __ffma2_rn(v2[b][j][k], v2[b][j][k], ss2);
-                  dt2 = __ffma2_rn(v2[b][j][k], q2[j][k], dt2);
-                }
+          for (int j = 0; j < NV; ++j) {
+            v2[b][j][0] = make_float2(bf16x2_lo(raw[j].x), bf16x2_hi(raw[j].x));
+            v2[b][j][1] = make_float2(bf16x2_lo(raw[j].y), bf16x2_hi(raw[j].y));
+            v2[b][j][2] = make_float2(bf16x2_lo(raw[j].z), bf16x2_hi(raw[j].z));
+            v2[b][j][3] = make_float2(bf16x2_lo(raw[j].w), bf16x2_hi(raw[j].w));
+            if (in_tail[j]) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                ss2 = __ffma2_rn(v2[b][j][k], v2[b][j][k], ss2);
+                dt2 = __ffma2_rn(v2[b][j][k], q2[j][k], dt2);
               }
-            } else {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) v2[b][j][k] = make_float2(0.f, 0.f);
             }
           }
         } else {
@@ -232,21 +255,25 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
 #pragma unroll
         for (int i = 0; i < 2 * B; ++i) tot[i] = __shfl_sync(0xffffffffu, keep, i * 8);
       } else {
-        float* mine = part_sm + buf * (2 * B * kRingMaxGroupWarps);
-        if ((lane & 7) == 0) mine[(lane >> 3) * kRingMaxGroupWarps + wig] = keep;
+        float4* mine = part_sm + buf * kRingMaxGroupWarps;
+        if ((lane & 7) == 0) reinterpret_cast<float*>(&mine[wig])[lane >> 3] = keep;
         group_sync(group, L);
 #pragma unroll
-        for (int i = 0; i < 2 * B; ++i) {
-          float t = 0.f;
-          for (int w = 0; w < G; ++w) t += mine[i * kRingMaxGroupWarps + w];
-          tot[i] = t;
+        for (int i = 0; i < 2 * B; ++i) tot[i] = 0.f;
+#pragma unroll
+        for (int w = 0; w < G; ++w) {
+          const float4 t = mine[w];
+          tot[0] += t.x;
+          tot[1] += t.y;
+          tot[2] += t.z;
+          tot[3] += t.w;
         }
       }
       // Every lane of the group has read its chunks of these stages: refill them.
       if (leader) {
         fence_proxy_async();
         in_flight -= nb;
-        while (to_issue > 0 && in_flight < nst) issue_one();
+        while (rows_to_issue > 0 && in_flight < nst) issue_one();
       }
 
       // Online softmax over the batch.
@@ -284,9 +311,9 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
           if (leader) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
         }
       }
-      use_stage += (uint32_t)nb;
-      if (use_stage >= (uint32_t)nst) {
-        use_stage -= (uint32_t)nst;
+      use_stage += nb;
+      if (use_stage >= nst) {
+        use_stage -= nst;
         use_phase ^= 1u;
       }
     }
@@ -324,6 +351,26 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   }
 }
 
+template <int G, int TAIL0>
+inline int launch_fwd_ring(const FwdParams& p, const FwdRingPlan& plan, int grid,
+                           cudaStream_t stream) {
+  if (int st = prepare_kernel(fwd_ring_kernel<G, TAIL0>, plan.smem_bytes)) return st;
+  fwd_ring_kernel<G, TAIL0><<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
+  return cudaGetLastError() == cudaSuccess ? 0 : 9;
+}
+
+template <int G>
+inline int launch_fwd_ring_tail(const FwdParams& p, const FwdRingPlan& plan, int grid,
+                                cudaStream_t stream) {
+  switch (plan.tail0) {
+    case 0: return launch_fwd_ring<G, 0>(p, plan, grid, stream);
+    case 1: return launch_fwd_ring<G, 1>(p, plan, grid, stream);
+    case 2: return launch_fwd_ring<G, 2>(p, plan, grid, stream);
+    case 3: return launch_fwd_ring<G, 3>(p, plan, grid, stream);
+    default: return launch_fwd_ring<G, -1>(p, plan, grid, stream);
+  }
+}
+
 inline int launch_fwd_tma(const FwdParams& p, int sms, cudaStream_t stream) {
   FwdRingPlan plan;
   if (!make_fwd_plan(p.S, p.D, p.R, &plan)) return 9;
@@ -331,14 +378,12 @@ inline int launch_fwd_tma(const FwdParams& p, int sms, cudaStream_t stream) {
   const int64_t wanted = (p.N + groups - 1) / groups;
   const int64_t cap = (int64_t)sms * plan.ctas_per_sm;
   const int grid = (int)(wanted < cap ? wanted : cap);
-  if (plan.cta_warps == 4) {
-    if (int st = prepare_kernel(fwd_ring_kernel<4>, plan.smem_bytes)) return st;
-    fwd_ring_kernel<4><<<grid, 128, plan.smem_bytes, stream>>>(p, plan);
-  } else {
-    if (int st = prepare_kernel(fwd_ring_kernel<8>, plan.smem_bytes)) return st;
-    fwd_ring_kernel<8><<<grid, 256, plan.smem_bytes, stream>>>(p, plan);
+  switch (plan.group_warps) {
+    case 1: return launch_fwd_ring_tail<1>(p, plan, grid, stream);
+    case 2: return launch_fwd_ring_tail<2>(p, plan, grid, stream);
+    case 4: return launch_fwd_ring_tail<4>(p, plan, grid, stream);
+    default: return launch_fwd_ring_tail<8>(p, plan, grid, stream);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }
 
 }  // namespace attnres_b200
