@@ -29,6 +29,15 @@ SIGNATURES = {
         c_void_p, c_int64, c_float, c_float,
         c_void_p, c_int64, c_void_p, c_void_p,
         c_uint32, c_void_p]),
+    "attnres_b200_backward_static_scratch": (c_int32, [
+        _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
+        c_int32, c_int64, c_int32, c_int32,
+        c_void_p, c_int64, c_float, c_float,
+        c_void_p, c_int64, c_int64,
+        c_void_p, c_void_p,
+        _PTR_ARRAY, _I64_ARRAY,
+        c_void_p, c_void_p,
+        c_uint32, c_void_p]),
     "attnres_b200_backward": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
         c_int32, c_int64, c_int32, c_int32,
@@ -110,6 +119,27 @@ def backward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_s
         None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
         partials_ptr, partial_rows, dq_bf16_ptr, dq_f32_ptr, flags, stream)
     check(status, "attnres_b200_backward")
+
+
+STATIC_SCRATCH_FLOATS = 2424832
+ERR_STATIC_SCRATCH = 12
+
+
+def backward_static_scratch(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr,
+                            query_stride, eps, scale, go_ptr, go_row_stride, go_feat_stride,
+                            logits_ptr, stats_ptr, dsrc_ptrs, dsrc_row_strides,
+                            dq_bf16_ptr, dq_f32_ptr, flags, stream) -> int:
+    """Backward for callers that cannot allocate the dquery workspace: the partial sums go
+    to a fixed array inside the library.  Returns the status code (0 = enqueued) instead of
+    raising, so a caller can fall back to ``backward`` on ERR_STATIC_SCRATCH.  The first
+    call on a device must happen outside stream capture; concurrent calls race."""
+    return load().attnres_b200_backward_static_scratch(
+        pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
+        S, N, D, R, query_ptr, query_stride, eps, scale,
+        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
+        None if dsrc_ptrs is None else pointer_array(dsrc_ptrs),
+        None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
+        dq_bf16_ptr, dq_f32_ptr, flags, stream)
 
 
 def error_flag(clear: bool = False) -> int:

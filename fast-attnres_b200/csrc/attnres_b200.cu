@@ -4,6 +4,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "generic_kernels.cuh"
@@ -139,6 +140,9 @@ extern "C" const char* attnres_b200_status_string(int status) {
     case ATTNRES_B200_ERR_CUDA: return "a CUDA runtime call failed";
     case ATTNRES_B200_ERR_BAD_FLAGS: return "unknown flag bits";
     case ATTNRES_B200_ERR_NOTHING_TO_DO: return "backward needs a value or a query gradient output";
+    case ATTNRES_B200_ERR_STATIC_SCRATCH:
+      return "shape needs more dquery scratch than the built-in array holds; pass a workspace to "
+             "attnres_b200_backward";
     default: return "unknown status";
   }
 }
@@ -303,4 +307,63 @@ extern "C" int attnres_b200_backward(
     if (cudaGetLastError() != cudaSuccess) return ATTNRES_B200_ERR_CUDA;
   }
   return ATTNRES_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward without a caller workspace: the dquery partials go to a fixed device array.
+
+namespace {
+
+// The only device memory the library owns.  In host code this name is a host-side handle,
+// not a device address; static_scratch_address() below asks the runtime for the address.
+static __device__ __align__(256) float g_static_dq_scratch[ATTNRES_B200_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+float* g_static_scratch_address[kMaxDevices] = {};
+
+// Device address of the array on the CURRENT device, looked up once per device.
+int static_scratch_address(int device, float** out) {
+  if (device < 0 || device >= kMaxDevices) return ATTNRES_B200_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    float* address = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_dq_scratch) != cudaSuccess ||
+        address == nullptr) {
+      cudaGetLastError();
+      return ATTNRES_B200_ERR_CUDA;
+    }
+    g_static_scratch_address[device] = address;
+  }
+  *out = g_static_scratch_address[device];
+  return ATTNRES_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int attnres_b200_backward_static_scratch(
+    const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
+    const float* logits, const float* stats,
+    void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
+    void* dq_bf16, float* dq_f32,
+    uint32_t flags, void* stream) {
+  if (int st = check_shape(S, N, D, R)) return st;
+  int device = 0;
+  if (int st = current_device(&device)) return st;
+  const int32_t rows = attnres_b200_dq_workspace_rows(N, S, D, R, device);
+  if (rows < 0) return -rows;
+  if ((int64_t)rows * R > (int64_t)ATTNRES_B200_STATIC_SCRATCH_FLOATS)
+    return ATTNRES_B200_ERR_STATIC_SCRATCH;
+  float* scratch = nullptr;
+  if (int st = static_scratch_address(device, &scratch)) return st;
+  // Every element of scratch[0 : grid*R] that the second stage sums is written by the first
+  // stage of this same call, so stale contents from earlier calls are never read.
+  return attnres_b200_backward(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query,
+                               query_stride, eps, scale, grad_out, go_row_stride, go_feat_stride,
+                               logits, stats, dsrc_ptrs, dsrc_row_stride, scratch, rows, dq_bf16,
+                               dq_f32, flags, stream);
 }

@@ -14,11 +14,13 @@
  *                   src/attnres/_kernels/fla_full_sources.py:752-894)
  *
  * Every entry point below takes plain pointers, sizes and a CUDA stream.  The
- * library owns no memory: the caller allocates inputs, outputs and the dquery
- * workspace and keeps them alive until the stream has run the work.  No entry
- * point synchronises, and every argument error is found on the host before a
- * kernel is launched.  Calls are re-entrant; calls on different streams may run
- * concurrently as long as they do not share output or workspace buffers.
+ * caller allocates inputs, outputs and the dquery workspace and keeps them alive
+ * until the stream has run the work; the library allocates nothing (the one
+ * piece of device memory it owns is the fixed scratch array documented at
+ * attnres_b200_backward_static_scratch).  No compute entry point synchronises,
+ * and every argument error is found on the host before a kernel is launched.
+ * Calls are re-entrant; calls on different streams may run concurrently as long
+ * as they do not share output or workspace buffers.
  *
  * Math (per flattened position n, sources s = 0..S-1, BF16 storage, FP32
  * arithmetic; validation/oracle.py:5-19):
@@ -56,6 +58,7 @@ extern "C" {
 #define ATTNRES_B200_ERR_CUDA 9               /* a CUDA runtime call failed (launch, attribute) */
 #define ATTNRES_B200_ERR_BAD_FLAGS 10
 #define ATTNRES_B200_ERR_NOTHING_TO_DO 11     /* backward with neither value nor query gradient */
+#define ATTNRES_B200_ERR_STATIC_SCRATCH 12    /* shape needs more than the built-in dquery scratch */
 
 /* `flags` bits. */
 #define ATTNRES_B200_FLAG_DEFAULT 0u
@@ -147,6 +150,49 @@ int attnres_b200_backward(
  */
 const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t aligned,
                                        int32_t backward);
+
+/*
+ * Backward read for callers that cannot hand the library a dquery workspace.
+ * It has no counterpart in the reference.
+ *
+ * Some hosts may not allocate device memory at the point where they call the
+ * operator: an inference or training runtime that reserves the whole GPU in
+ * one arena at start-up and forbids cudaMalloc afterwards, a plugin running
+ * inside someone else's captured region or real-time loop, or a binding from a
+ * language whose tensors cannot be created from inside a callback.  For them the
+ * FP32 [rows, R] scratch of the two-stage dquery reduction lives inside the
+ * library, in a fixed device array of ATTNRES_B200_STATIC_SCRATCH_FLOATS floats
+ * (9.25 MiB, held by every GPU that loads the library until the process exits).
+ *
+ * Arguments and results are those of attnres_b200_backward without
+ * `dq_partials` / `dq_partial_rows`; inputs and outputs still belong to the
+ * caller.  The call allocates nothing and frees nothing.
+ *
+ *   - Limit: attnres_b200_dq_workspace_rows(N, S, D, R, device) * R must not
+ *     exceed ATTNRES_B200_STATIC_SCRATCH_FLOATS (any N up to R = 2048; larger R
+ *     only with few rows).  Otherwise nothing is launched and the call returns
+ *     ATTNRES_B200_ERR_STATIC_SCRATCH; use attnres_b200_backward instead.
+ *   - The first call on each device looks up the device address of the array
+ *     (one driver query, cached per device).  Make that first call outside any
+ *     CUDA stream capture.
+ *   - All calls on a device share the one array.  Its contents are whatever the
+ *     previous call left; this is harmless because every element the second
+ *     stage reads is written by the first stage of the same call, so nothing has
+ *     to be cleared.  Two calls that overlap on the GPU (different streams, or
+ *     graphs replayed concurrently) race on the array: serialise them.
+ */
+#define ATTNRES_B200_STATIC_SCRATCH_FLOATS 2424832 /* 1184 rows x 2048 */
+int attnres_b200_backward_static_scratch(
+    const void* const* src_ptrs, const int64_t* src_row_stride,
+    const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
+    const float* logits, const float* stats,
+    void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
+    void* dq_bf16, float* dq_f32,
+    uint32_t flags, void* stream);
 
 /*
  * Diagnostics (no counterpart in the reference).  The TMA-staged kernels bound
