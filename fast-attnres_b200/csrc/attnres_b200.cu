@@ -294,10 +294,13 @@ extern "C" int attnres_b200_backward(
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
   int grid = max_rows;
-  int st;
-  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC) && tma_bwd_supported(S, D, R)) {
+  int st = ATTNRES_B200_ERR_CUDA;
+  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC) && tma_bwd_supported(S, D, R))
     st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
-  } else {
+  if (st != ATTNRES_B200_OK) {
+    // Not eligible, or the launch was refused (for example a cluster shape this device
+    // cannot co-schedule): the layout-generic kernel takes any input.
+    grid = max_rows;
     st = dispatch_bwd_generic(p, vec, grid, cs);
   }
   if (st != ATTNRES_B200_OK) return st;

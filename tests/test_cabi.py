@@ -98,7 +98,8 @@ def test_kernel_family_selection_is_a_pure_host_decision():
     assert _native.kernel_family(16, 4096, 1024, True, True) == "tma"
     assert _native.kernel_family(9, 2048, 2048, False, True) == "generic"
     assert _native.kernel_family(9, 3000, 127, True, False) == "generic"
-    assert _native.kernel_family(49, 4096, 4096, True, True) == "generic"   # row exceeds shared memory
+    assert _native.kernel_family(49, 4096, 4096, True, True) == "tma"       # a 2-CTA cluster shares the row
+    assert _native.kernel_family(129, 8192, 8192, True, True) == "generic"  # 2.1 MB row: beyond 8 CTAs
     assert _native.kernel_family(49, 4096, 4096, True, False) == "tma"
     assert _native.kernel_family(2, 1024, 1024, False, False) == "generic"
     assert _native.kernel_family(0, 1024, 1024, True, False) == "invalid"

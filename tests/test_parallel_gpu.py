@@ -1,0 +1,77 @@
+"""Position sharding on real GPUs (needs two devices; skipped on a one-GPU box).
+
+Each rank runs the CUDA kernels on its own rows; the FP32 query gradients meet in one NCCL
+all-reduce and are rounded to BF16 once.  The result must equal the unsharded read: outputs and
+value gradients bit for bit (positions are independent), the query gradient within one BF16
+rounding of the FP32 reassociation.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")]
+
+
+def _free_port() -> int:
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def _inputs(device):
+    generator = torch.Generator(device="cpu").manual_seed(20260827)
+    values = torch.randn(6, 1000, 1024, generator=generator).to(torch.bfloat16).to(device)
+    query = (torch.randn(256, generator=generator) * 0.25).to(torch.bfloat16).to(device)
+    upstream = torch.randn(1000, 1024, generator=generator).to(torch.bfloat16).to(device)
+    return values, query, upstream
+
+
+def _worker(rank, world, port, as_list, results):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    for entry in (root, root / "fast-attnres_b200"):
+        if str(entry) not in sys.path:
+            sys.path.insert(0, str(entry))
+    from attnres.parallel import shard_rows, sharded_attnres
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        values, query, upstream = _inputs(f"cuda:{rank}")
+        start, stop = shard_rows(values.shape[1], world, rank)
+        mine = values[:, start:stop].contiguous().requires_grad_()
+        q = query.clone().requires_grad_()
+        arg = tuple(mine.unbind(0)) if as_list else mine
+        out = sharded_attnres(arg, q, scale=0.0625)
+        dv, dq = torch.autograd.grad(out, (mine, q), upstream[start:stop])
+        torch.cuda.synchronize()
+        results[rank] = (start, stop, out.cpu(), dv.cpu(), dq.cpu())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("as_list", [False, True], ids=["packed", "list"])
+def test_two_gpu_sharding_equals_the_unsharded_read(as_list):
+    from attnres import attnres
+    world, port = 2, _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, port, as_list, results), nprocs=world, join=True)
+    values, query, upstream = _inputs("cuda:0")
+    values.requires_grad_()
+    query.requires_grad_()
+    out = attnres(values, query, scale=0.0625)
+    dv, dq = torch.autograd.grad(out, (values, query), upstream)
+    for rank in range(world):
+        start, stop, out_r, dv_r, dq_r = results[rank]
+        assert torch.equal(out_r, out[start:stop].cpu())
+        assert torch.equal(dv_r, dv[:, start:stop].cpu())
+        assert torch.equal(dq_r, results[0][4]), "ranks disagree on the reduced query gradient"
+        torch.testing.assert_close(dq_r.float(), dq.cpu().float(), rtol=2**-7, atol=2**-7)
