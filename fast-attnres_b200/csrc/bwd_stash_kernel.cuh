@@ -248,7 +248,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // MULTI = false fixes cluster size and source groups at 1 at compile time (the common case).
 // MAXT is the CTA size the instance is compiled for: narrow CTAs may use about 112 registers
 // per thread, the 17-warp CTA of a 4096-wide slice is held to 96.
-template <int NV, bool MULTI, int MAXT>
+// FULL: R == D and the slice fills the warps exactly, so no chunk needs a predicate.
+template <int NV, bool MULTI, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : MAXT <= 288 ? 2 : 1)
 bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdPlan plan) {
   constexpr int GK = kStashSliceChunks;
@@ -340,8 +341,8 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     own_chunk[j] = wslice * 32 + lane + j * W * 32;
-    own_valid[j] = own_chunk[j] < CHs;
-    own_tail[j] = own_valid[j] && chunk_base + own_chunk[j] >= c0;
+    own_valid[j] = FULL ? true : own_chunk[j] < CHs;
+    own_tail[j] = FULL ? true : (own_valid[j] && chunk_base + own_chunk[j] >= c0);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo = 0.f, hi = 0.f;
@@ -402,7 +403,7 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
             unpack8_pairs(vrow[c], v);
 #pragma unroll
             for (int e = 0; e < 4; ++e) dw2 = __ffma2_rn(v[e], gs[k][e], dw2);
-            if (chunk_base + c >= c0) {
+            if (FULL || chunk_base + c >= c0) {
 #pragma unroll
               for (int e = 0; e < 4; ++e) ss2 = __ffma2_rn(v[e], v[e], ss2);
             }
@@ -508,8 +509,8 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
 #pragma unroll
           for (int e = 0; e < 4; ++e) dv[e] = __fmul2_rn(ps2, g2[j][e]);
           if (own_tail[j]) {
-            // Observe the copy's completion in this thread before reading its bytes.
-            mbar_wait(&full_row[1 + s], parity, abort_flag);
+            // No wait here: in sweep 1 some warp of this CTA observed the completion of every
+            // source's copy, and all warps have met at the named barrier since then.
             float2 v[4];
             unpack8_pairs(vrow[own_chunk[j]], v);
 #pragma unroll
@@ -552,12 +553,12 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
   }
 }
 
-template <int NV, bool MULTI, int MAXT>
+template <int NV, bool MULTI, int MAXT, bool FULL>
 inline int launch_bwd_stash(const BwdParams& p, const BwdPlan& plan, int grid, int threads,
                             cudaStream_t stream) {
-  if (int st = prepare_kernel(bwd_tma_kernel<NV, MULTI, MAXT>, plan.smem_bytes)) return st;
+  if (int st = prepare_kernel(bwd_tma_kernel<NV, MULTI, MAXT, FULL>, plan.smem_bytes)) return st;
   if (plan.cluster == 1) {
-    bwd_tma_kernel<NV, MULTI, MAXT><<<grid, threads, plan.smem_bytes, stream>>>(p, plan);
+    bwd_tma_kernel<NV, MULTI, MAXT, FULL><<<grid, threads, plan.smem_bytes, stream>>>(p, plan);
   } else {
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)grid, 1, 1);
@@ -571,7 +572,7 @@ inline int launch_bwd_stash(const BwdParams& p, const BwdPlan& plan, int grid, i
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    if (cudaLaunchKernelEx(&config, bwd_tma_kernel<NV, MULTI, MAXT>, p, plan) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&config, bwd_tma_kernel<NV, MULTI, MAXT, FULL>, p, plan) != cudaSuccess) {
       cudaGetLastError();
       return 9;
     }
@@ -595,9 +596,13 @@ inline int launch_bwd_tma(const BwdParams& p, int sms, int max_rows, int* rows_o
   const int nv = stash_chunks_per_thread(p.D / plan.cluster);
   const bool multi = plan.cluster > 1 || plan.source_groups > 1;
   int st;
-#define ATTNRES_LAUNCH_STASH(NVV, MAXT)                                                   \
-  st = multi ? launch_bwd_stash<NVV, true, MAXT>(p, plan, grid, threads, stream)          \
-             : launch_bwd_stash<NVV, false, MAXT>(p, plan, grid, threads, stream)
+  const int slice_chunks = (p.D / 8) / plan.cluster;
+  const bool full = p.R == p.D && slice_chunks == 32 * plan.slice_warps * nv;
+#define ATTNRES_LAUNCH_STASH(NVV, MAXT)                                                          \
+  st = multi ? (full ? launch_bwd_stash<NVV, true, MAXT, true>(p, plan, grid, threads, stream)   \
+                     : launch_bwd_stash<NVV, true, MAXT, false>(p, plan, grid, threads, stream)) \
+             : (full ? launch_bwd_stash<NVV, false, MAXT, true>(p, plan, grid, threads, stream)  \
+                     : launch_bwd_stash<NVV, false, MAXT, false>(p, plan, grid, threads, stream))
   if (nv == 1) {
     if (threads <= 160) { ATTNRES_LAUNCH_STASH(1, 160); }
     else if (threads <= 288) { ATTNRES_LAUNCH_STASH(1, 288); }
