@@ -327,7 +327,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
 
     # ---- end to end: pinned host buffers -> public API -> host results
     e2e = (run_e2e(args, cells, device, distributed) if not args.skip_e2e
-           else {"ms_per_step": float("nan"), "h2d": 0, "d2h": 0, "steps": 0})
+           else {"ms_per_step": float("inf"), "h2d": 0, "d2h": 0, "steps": 0})
     if distributed:
         worst = torch.tensor([e2e["ms_per_step"]], device=device, dtype=torch.float64)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
@@ -353,8 +353,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "gbs": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9, 1),
             "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
         })
-    cpu_rate, cpu_seconds, threads = (cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS) if not args.skip_cpu
-                                      else (float("nan"), 0.0, 0))
+    # The CPU oracle is timed at N = 1 only (under torchrun every rank is held to one thread).
+    run_cpu = not args.skip_cpu and world == 1
+    cpu_rate, cpu_seconds, threads = (cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS) if run_cpu
+                                      else (None, 0.0, 0))
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -375,9 +377,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
                 "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e["ms_per_step"],
                 "steps": e2e["steps"]},
-        "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"PyTorch oracle port, all 18 cells at {CPU_SAMPLE_ROWS} rows "
-                                   f"each ({cpu_seconds:.1f} s of CPU work)"},
+        "cpu_baseline": ({"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                          "sample": f"PyTorch oracle port, all 18 cells at {CPU_SAMPLE_ROWS} rows "
+                                    f"each ({cpu_seconds:.1f} s of CPU work)"} if run_cpu else None),
         "gpu_launches": args.steps * len(cells) * 3,
         "clocks": clocks.summary(),
         "cells": per_cell,

@@ -39,7 +39,7 @@ namespace attnres_b200 {
 
 constexpr int kStashSliceChunks = 4;  // chunks of the row a lane covers in sweep 1
 constexpr int kStashMaxBuffers = 4;
-constexpr int kStashMaxCluster = 8;
+constexpr int kStashMaxCluster = 2;  // larger clusters measured slower than the generic kernel
 // Registers per thread of the compiled instances, for the occupancy estimate.
 inline int stash_regs_per_thread(int threads) { return threads <= 160 ? 100 : threads <= 288 ? 112 : 96; }
 
@@ -107,10 +107,11 @@ inline bool make_bwd_plan(int S, int D, int R, BwdPlan* plan) {
     const int W = p.slice_warps;
     const uint32_t coef_bytes = (uint32_t)S * 16u;
     const uint32_t zl_bytes = align_up((uint32_t)(S + 2) * 4u, 16);
-    const uint32_t xsum_bytes = C > 1 ? 2u * (uint32_t)C * (uint32_t)S * 8u : 0u;
+    const uint32_t xsum_bytes = 0u;
+    const uint32_t part_copies = C > 1 ? 2u * (uint32_t)C : 1u;
     const uint32_t bars_bytes = (uint32_t)kStashMaxBuffers * (uint32_t)(S + 1) * 2u * 8u + 16u;
     auto fixed_bytes = [&](int parts) {
-      return align_up((uint32_t)S * (uint32_t)parts * 8u, 16) + coef_bytes + zl_bytes + xsum_bytes +
+      return align_up(part_copies * (uint32_t)S * (uint32_t)parts * 8u, 16) + coef_bytes + zl_bytes + xsum_bytes +
              bars_bytes + 16u + 64u;
     };
     // An SM offers 228 KB of shared memory; every resident CTA reserves 1 KB of it.
@@ -153,7 +154,7 @@ inline bool make_bwd_plan(int S, int D, int R, BwdPlan* plan) {
     p.ctas_per_sm = ctas;
     uint32_t off = (uint32_t)buffers * p.row_buffer_bytes;
     p.off_part = off;
-    off += align_up((uint32_t)S * (uint32_t)p.parts * 8u, 16);
+    off += align_up(part_copies * (uint32_t)S * (uint32_t)p.parts * 8u, 16);
     p.off_coef = off;
     off += coef_bytes;
     p.off_zl = off;
@@ -204,9 +205,8 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t ra
   return remote;
 }
 
-__device__ __forceinline__ void cluster_store_f2(uint32_t remote_addr, float a, float b) {
-  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote_addr), "f"(a), "f"(b)
-               : "memory");
+__device__ __forceinline__ void cluster_store_f1(uint32_t remote_addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(a) : "memory");
 }
 
 __device__ __forceinline__ void cluster_arrive_remote(uint32_t remote_bar) {
@@ -248,18 +248,20 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return true;
 }
 
-// MULTI = false fixes cluster size and source groups at 1 at compile time (the common case).
+// CL is the cluster size (1 or 2) and GROUPS says whether source groups are in use; both are
+// compile-time so the common single-CTA, single-group case carries none of that code.
 // MAXT is the CTA size the instance is compiled for: narrow CTAs may use about 112 registers
 // per thread, the 17-warp CTA of a 4096-wide slice is held to 96.
 // FULL: R == D and the slice fills the warps exactly, so no chunk needs a predicate.
-template <int NV, bool MULTI, int MAXT, bool FULL>
+template <int NV, int CL, bool GROUPS, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : MAXT <= 288 ? 2 : 1)
 bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdPlan plan) {
   constexpr int GK = kStashSliceChunks;
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int C = MULTI ? plan.cluster : 1, W = plan.slice_warps;
-  const int SG = MULTI ? plan.source_groups : 1;
+  constexpr int C = CL;
+  const int W = plan.slice_warps;
+  const int SG = GROUPS ? plan.source_groups : 1;
   const int WT = W * SG, T = WT * 32;
   const int S = p.S, D = p.D, R = p.R;
   const int c0 = (D - R) / 8;            // first tail chunk of the full row
@@ -269,10 +271,9 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
   const int64_t position0 = blockIdx.x / C, position_step = gridDim.x / C;
   const int NRB = plan.row_buffers, NP = plan.parts, slots = S + 1;
   const uint32_t slot_bytes = plan.slot_bytes;
-  float* part_sm = reinterpret_cast<float*>(smem + plan.off_part);    // [S][NP][2] (ss, dw)
+  float* part_sm = reinterpret_cast<float*>(smem + plan.off_part);    // [1 or 2][S][C][NP][2] (ss, dw)
   float4* coef_sm = reinterpret_cast<float4*>(smem + plan.off_coef);  // [S] (p, ca, cb, -)
   float* zl_sm = reinterpret_cast<float*>(smem + plan.off_zl);        // [S] logits, max, 1/sum
-  float2* xsum_sm = reinterpret_cast<float2*>(smem + plan.off_xsum);  // [2][C][S] (ss, dw)
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + plan.off_bars);  // [NRB][slots]
   uint64_t* empty_bar = full_bar + kStashMaxBuffers * slots;
   uint64_t* xchg_bar = empty_bar + kStashMaxBuffers * slots;  // [2]
@@ -286,8 +287,8 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
         mbar_init(&empty_bar[b * slots + slot], slot == 0 ? WT : W);
       }
     }
-    mbar_init(&xchg_bar[0], C);
-    mbar_init(&xchg_bar[1], C);
+    mbar_init(&xchg_bar[0], C * WT);
+    mbar_init(&xchg_bar[1], C * WT);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -379,6 +380,10 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
+    // In a cluster the partial sums alternate between two buffers: a peer may already be
+    // writing the next position's sums while this CTA still reads the current ones.
+    float* part_row = part_sm + (C > 1 ? (xchg_count & 1u) * (uint32_t)(S * C * NP * 2) : 0u);
+
     // ---- sweep 1
     mbar_wait(&full_row[0], parity, abort_flag);
     const uint4* grow_sm = reinterpret_cast<const uint4*>(base);
@@ -421,61 +426,52 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
         keep += __shfl_xor_sync(0xffffffffu, keep, 4);
         keep += __shfl_xor_sync(0xffffffffu, keep, 2);
         keep += __shfl_xor_sync(0xffffffffu, keep, 1);
-        if ((lane & 15) == 0) part_sm[(s * NP + my_part) * 2 + (lane >> 4)] = keep;
+        // Partial sums are laid out [S][C][NP][2]; in a cluster every CTA gets a copy of this
+        // CTA's entry straight away, so the exchange overlaps the rest of sweep 1.
+        if ((lane & 15) == 0) {
+          float* dst = part_row + ((s * C + crank) * NP + my_part) * 2 + (lane >> 4);
+          if (C > 1) {
+            for (int t = 0; t < C; ++t) cluster_store_f1(cluster_map(smem_addr(dst), (uint32_t)t), keep);
+          } else {
+            *dst = keep;
+          }
+        }
       }
     }
-    consumer_sync(T);
+    const uint32_t xbuf = xchg_count & 1u, xpar = (xchg_count >> 1) & 1u;
+    if (C > 1) {
+      // Every warp of every CTA of the cluster announces its partial sums on each CTA's
+      // exchange barrier; only warp 0 waits for the full count.
+      asm volatile("fence.acq_rel.cluster;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        for (int t = 0; t < C; ++t)
+          cluster_arrive_remote(cluster_map(smem_addr(&xchg_bar[xbuf]), (uint32_t)t));
+      }
+      ++xchg_count;
+    } else {
+      consumer_sync(T);
+    }
 
     // ---- delta and the per-source coefficients (warp 0; lane l takes sources l, l+32, ...)
     if (warp == 0) {
       asm volatile("cp.async.wait_all;" ::: "memory");
       __syncwarp();
-      if (C > 1) {
-        // Hand this CTA's sums to every CTA of the cluster (itself included), announce them
-        // and wait for all C contributions; they are added in rank order below.
-        const uint32_t xbuf = xchg_count & 1u, xpar = (xchg_count >> 1) & 1u;
-        float2* mine = xsum_sm + (xbuf * C + crank) * S;
-        for (int s = lane; s < S; s += 32) {
-          float ss = 0.f, dw = 0.f;
-          for (int part = 0; part < NP; ++part) {
-            const float2 v = *reinterpret_cast<const float2*>(&part_sm[(s * NP + part) * 2]);
-            ss += v.x;
-            dw += v.y;
-          }
-          for (int t = 0; t < C; ++t)
-            cluster_store_f2(cluster_map(smem_addr(mine + s), (uint32_t)t), ss, dw);
-        }
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          for (int t = 0; t < C; ++t)
-            cluster_arrive_remote(cluster_map(smem_addr(&xchg_bar[xbuf]), (uint32_t)t));
-        }
-        mbar_wait_cluster(&xchg_bar[xbuf], xpar, abort_flag);
-      }
+      if (C > 1) mbar_wait_cluster(&xchg_bar[xbuf], xpar, abort_flag);
       const float row_max = zl_sm[S], inv_sum = zl_sm[S + 1];
       float local = 0.f;
       for (int s = lane; s < S; s += 32) {
         float ss = 0.f, dw = 0.f;
-        if (C > 1) {
-          const float2* all = xsum_sm + ((xchg_count & 1u) * C) * S + s;
-          for (int t = 0; t < C; ++t) {
-            ss += all[t * S].x;
-            dw += all[t * S].y;
-          }
-        } else {
-          for (int part = 0; part < NP; ++part) {
-            const float2 v = *reinterpret_cast<const float2*>(&part_sm[(s * NP + part) * 2]);
-            ss += v.x;
-            dw += v.y;
-          }
+        for (int part = 0; part < C * NP; ++part) {  // rank-major: the same order in every CTA
+          const float2 v = *reinterpret_cast<const float2*>(&part_row[(s * C * NP + part) * 2]);
+          ss += v.x;
+          dw += v.y;
         }
         const float z = zl_sm[s];
         const float prob = __expf(z - row_max) * inv_sum;
         coef_sm[s] = make_float4(prob, dw, rsqrtf(ss * inv_rank + p.eps), z);
         local = fmaf(prob, dw, local);
       }
-      if (C > 1) ++xchg_count;
       const float delta = warp_sum(local);
       for (int s = lane; s < S; s += 32) {
         const float4 t = coef_sm[s];  // (p, dw, inv_rms, z) written by this lane above
@@ -556,12 +552,12 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
   }
 }
 
-template <int NV, bool MULTI, int MAXT, bool FULL>
+template <int NV, int CL, bool GROUPS, int MAXT, bool FULL>
 inline int launch_bwd_stash(const BwdParams& p, const BwdPlan& plan, int grid, int threads,
                             cudaStream_t stream) {
-  if (int st = prepare_kernel(bwd_tma_kernel<NV, MULTI, MAXT, FULL>, plan.smem_bytes)) return st;
+  if (int st = prepare_kernel(bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL>, plan.smem_bytes)) return st;
   if (plan.cluster == 1) {
-    bwd_tma_kernel<NV, MULTI, MAXT, FULL><<<grid, threads, plan.smem_bytes, stream>>>(p, plan);
+    bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL><<<grid, threads, plan.smem_bytes, stream>>>(p, plan);
   } else {
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)grid, 1, 1);
@@ -575,7 +571,7 @@ inline int launch_bwd_stash(const BwdParams& p, const BwdPlan& plan, int grid, i
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    if (cudaLaunchKernelEx(&config, bwd_tma_kernel<NV, MULTI, MAXT, FULL>, p, plan) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&config, bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL>, p, plan) != cudaSuccess) {
       cudaGetLastError();
       return 9;
     }
@@ -597,24 +593,28 @@ inline int launch_bwd_tma(const BwdParams& p, int sms, int max_rows, int* rows_o
   if (streams < 1) return 9;
   const int grid = (int)streams * plan.cluster;
   const int nv = stash_chunks_per_thread(p.D / plan.cluster);
-  const bool multi = plan.cluster > 1 || plan.source_groups > 1;
-  int st;
+  const bool groups = plan.source_groups > 1;
   const int slice_chunks = (p.D / 8) / plan.cluster;
   const bool full = p.R == p.D && slice_chunks == 32 * plan.slice_warps * nv;
-#define ATTNRES_LAUNCH_STASH(NVV, MAXT)                                                          \
-  st = multi ? (full ? launch_bwd_stash<NVV, true, MAXT, true>(p, plan, grid, threads, stream)   \
-                     : launch_bwd_stash<NVV, true, MAXT, false>(p, plan, grid, threads, stream)) \
-             : (full ? launch_bwd_stash<NVV, false, MAXT, true>(p, plan, grid, threads, stream)  \
-                     : launch_bwd_stash<NVV, false, MAXT, false>(p, plan, grid, threads, stream))
+  int st;
+#define ATTNRES_LAUNCH_STASH4(NVV, CLV, MAXT)                                                     \
+  st = groups ? (full ? launch_bwd_stash<NVV, CLV, true, MAXT, true>(p, plan, grid, threads, stream)   \
+                      : launch_bwd_stash<NVV, CLV, true, MAXT, false>(p, plan, grid, threads, stream)) \
+              : (full ? launch_bwd_stash<NVV, CLV, false, MAXT, true>(p, plan, grid, threads, stream)  \
+                      : launch_bwd_stash<NVV, CLV, false, MAXT, false>(p, plan, grid, threads, stream))
+#define ATTNRES_LAUNCH_STASH(NVV, MAXT)                            \
+  if (plan.cluster == 1) { ATTNRES_LAUNCH_STASH4(NVV, 1, MAXT); }   \
+  else { ATTNRES_LAUNCH_STASH4(NVV, 2, MAXT); }
   if (nv == 1) {
-    if (threads <= 160) { ATTNRES_LAUNCH_STASH(1, 160); }
-    else if (threads <= 288) { ATTNRES_LAUNCH_STASH(1, 288); }
-    else { ATTNRES_LAUNCH_STASH(1, 544); }
+    if (threads <= 160) { ATTNRES_LAUNCH_STASH(1, 160) }
+    else if (threads <= 288) { ATTNRES_LAUNCH_STASH(1, 288) }
+    else { ATTNRES_LAUNCH_STASH(1, 544) }
   } else {
-    if (threads <= 160) { ATTNRES_LAUNCH_STASH(2, 160); }
-    else if (threads <= 288) { ATTNRES_LAUNCH_STASH(2, 288); }
-    else { ATTNRES_LAUNCH_STASH(2, 544); }
+    if (threads <= 160) { ATTNRES_LAUNCH_STASH(2, 160) }
+    else if (threads <= 288) { ATTNRES_LAUNCH_STASH(2, 288) }
+    else { ATTNRES_LAUNCH_STASH(2, 544) }
   }
+#undef ATTNRES_LAUNCH_STASH4
 #undef ATTNRES_LAUNCH_STASH
   *rows_out = (int)streams * plan.source_groups;
   return st;
