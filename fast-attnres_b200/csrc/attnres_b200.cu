@@ -10,6 +10,7 @@
 #include "generic_kernels.cuh"
 #include "fwd_ring_kernel.cuh"
 #include "bwd_stash_kernel.cuh"
+#include "bwd_ring_kernel.cuh"
 
 namespace attnres_b200 {
 namespace {
@@ -151,7 +152,7 @@ extern "C" const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t 
                                                   int32_t aligned, int32_t backward) {
   if (check_shape(S, 1, D, R) != ATTNRES_B200_OK) return "invalid";
   if (!aligned) return "generic";
-  if (backward) return tma_bwd_supported(S, D, R) ? "tma" : "generic";
+  if (backward) return (bwd_ring_supported(S, D, R) || tma_bwd_supported(S, D, R)) ? "tma" : "generic";
   return tma_fwd_supported(S, D, R) ? "tma" : "generic";
 }
 
@@ -295,8 +296,12 @@ extern "C" int attnres_b200_backward(
 
   int grid = max_rows;
   int st = ATTNRES_B200_ERR_CUDA;
-  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC) && tma_bwd_supported(S, D, R))
-    st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
+  if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC)) {
+    // Short source lists keep the whole position in registers; longer ones stage it.
+    if (bwd_ring_supported(S, D, R)) st = launch_bwd_ring(p, sms, max_rows, &grid, cs);
+    if (st != ATTNRES_B200_OK && tma_bwd_supported(S, D, R))
+      st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
+  }
   if (st != ATTNRES_B200_OK) {
     // Not eligible, or the launch was refused (for example a cluster shape this device
     // cannot co-schedule): the layout-generic kernel takes any input.
