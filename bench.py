@@ -12,7 +12,8 @@ from L2 between timed passes.
 
 With N > 1 (torchrun) every rank owns its own 16 384 positions of every cell
 (position sharding, no data-path collective; weak scaling) and the FP32 query
-gradient of every cell is all-reduced over NCCL before the BF16 cast.
+gradients of all cells are summed over NCCL (one bucketed all-reduce per step) before the
+BF16 cast.
 
 Printed JSON (rank 0, one line): whole-job tokens/s (`value`), the HBM roofline
 of the dominant (backward) kernel, the same metric end to end from pinned host
@@ -266,6 +267,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     upstreams = {d: torch.randn(ROWS, d, device=device, dtype=torch.bfloat16, generator=generator)
                  for d in WIDTHS}
     cells = [Cell(s, d, device, generator, grad_buffer, out_buffer, upstreams[d]) for s, d in CELLS]
+    # The query gradients of all cells live in one flat FP32 bucket (and one BF16 bucket), so
+    # the cross-rank sum of a step is ONE all-reduce, as a data-parallel framework buckets them.
+    flat32 = torch.empty(sum(c.D for c in cells), device=device, dtype=torch.float32)
+    flat16 = torch.empty_like(flat32, dtype=torch.bfloat16)
+    offset = 0
+    for cell in cells:
+        cell.dq32, cell.dq = flat32[offset:offset + cell.D], flat16[offset:offset + cell.D]
+        offset += cell.D
     for cell in cells:
         cell.capture(distributed)
     torch.cuda.synchronize()
@@ -288,9 +297,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             cell.bwd_graph.replay()
             if bwd_events:
                 bwd_events[index][1].record()
-            if distributed:
-                dist.all_reduce(cell.dq32)
-                cell.dq.copy_(cell.dq32)
+        if distributed:
+            dist.all_reduce(flat32)
+            flat16.copy_(flat32)
 
     def barrier():
         if distributed:
