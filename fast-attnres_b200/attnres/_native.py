@@ -9,8 +9,9 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 FLAG_FORCE_GENERIC = 1
+FLAG_PREFER_STREAM = 2
 LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / "libattnres_b200.so"
 
 _PTR_ARRAY = ctypes.POINTER(c_void_p)
@@ -27,14 +28,15 @@ SIGNATURES = {
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
         c_int32, c_int64, c_int32, c_int32,
         c_void_p, c_int64, c_float, c_float,
-        c_void_p, c_int64, c_void_p, c_void_p,
+        c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
         c_uint32, c_void_p]),
+    "attnres_b200_wants_output_residual": (c_int32, [c_int32, c_int32, c_int32]),
     "attnres_b200_backward_static_scratch": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
         c_int32, c_int64, c_int32, c_int32,
         c_void_p, c_int64, c_float, c_float,
         c_void_p, c_int64, c_int64,
-        c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p,
         _PTR_ARRAY, _I64_ARRAY,
         c_void_p, c_void_p,
         c_uint32, c_void_p]),
@@ -43,7 +45,7 @@ SIGNATURES = {
         c_int32, c_int64, c_int32, c_int32,
         c_void_p, c_int64, c_float, c_float,
         c_void_p, c_int64, c_int64,
-        c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p,
         _PTR_ARRAY, _I64_ARRAY,
         c_void_p, c_int32,
         c_void_p, c_void_p,
@@ -92,12 +94,18 @@ def int64_array(values) -> ctypes.Array:
 
 
 def forward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_stride,
-            eps, scale, out_ptr, out_row_stride, logits_ptr, stats_ptr, flags, stream) -> None:
+            eps, scale, out_ptr, out_row_stride, logits_ptr, stats_ptr, flags, stream,
+            residual_ptr=None) -> None:
     status = load().attnres_b200_forward(
         pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
         S, N, D, R, query_ptr, query_stride, eps, scale,
-        out_ptr, out_row_stride, logits_ptr, stats_ptr, flags, stream)
+        out_ptr, out_row_stride, residual_ptr, logits_ptr, stats_ptr, flags, stream)
     check(status, "attnres_b200_forward")
+
+
+def wants_output_residual(S, D, R) -> bool:
+    """Whether the backward of this shape is faster with the forward's output and residual."""
+    return bool(load().attnres_b200_wants_output_residual(S, D, R))
 
 
 def dq_workspace_rows(N, S, D, R, device_index) -> int:
@@ -110,11 +118,11 @@ def dq_workspace_rows(N, S, D, R, device_index) -> int:
 def backward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_stride,
              eps, scale, go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
              dsrc_ptrs, dsrc_row_strides, partials_ptr, partial_rows,
-             dq_bf16_ptr, dq_f32_ptr, flags, stream) -> None:
+             dq_bf16_ptr, dq_f32_ptr, flags, stream, out_ptr=None, residual_ptr=None) -> None:
     status = load().attnres_b200_backward(
         pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
         S, N, D, R, query_ptr, query_stride, eps, scale,
-        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
+        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr, out_ptr, residual_ptr,
         None if dsrc_ptrs is None else pointer_array(dsrc_ptrs),
         None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
         partials_ptr, partial_rows, dq_bf16_ptr, dq_f32_ptr, flags, stream)
@@ -128,7 +136,8 @@ ERR_STATIC_SCRATCH = 12
 def backward_static_scratch(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr,
                             query_stride, eps, scale, go_ptr, go_row_stride, go_feat_stride,
                             logits_ptr, stats_ptr, dsrc_ptrs, dsrc_row_strides,
-                            dq_bf16_ptr, dq_f32_ptr, flags, stream) -> int:
+                            dq_bf16_ptr, dq_f32_ptr, flags, stream, out_ptr=None,
+                            residual_ptr=None) -> int:
     """Backward for callers that cannot allocate the dquery workspace: the partial sums go
     to a fixed array inside the library.  Returns the status code (0 = enqueued) instead of
     raising, so a caller can fall back to ``backward`` on ERR_STATIC_SCRATCH.  The first
@@ -136,7 +145,7 @@ def backward_static_scratch(src_ptrs, row_strides, feat_strides, S, N, D, R, que
     return load().attnres_b200_backward_static_scratch(
         pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
         S, N, D, R, query_ptr, query_stride, eps, scale,
-        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr,
+        go_ptr, go_row_stride, go_feat_stride, logits_ptr, stats_ptr, out_ptr, residual_ptr,
         None if dsrc_ptrs is None else pointer_array(dsrc_ptrs),
         None if dsrc_row_strides is None else int64_array(dsrc_row_strides),
         dq_bf16_ptr, dq_f32_ptr, flags, stream)

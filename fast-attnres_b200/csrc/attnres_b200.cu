@@ -11,6 +11,7 @@
 #include "fwd_ring_kernel.cuh"
 #include "bwd_stash_kernel.cuh"
 #include "bwd_ring_kernel.cuh"
+#include "bwd_stream_kernel.cuh"
 
 namespace attnres_b200 {
 namespace {
@@ -120,6 +121,15 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
 
 constexpr int kWorkspaceRowsPerSm = 8;
 
+// The streaming backward pays 6*D extra bytes per position; it wins where the staged
+// backward is held to one CTA per SM (or needs a cluster, or does not fit at all).
+bool wants_output_residual(int S, int D, int R) {
+  if (S <= 4 || !bwd_stream_supported(S, D, R)) return false;
+  BwdPlan stash;
+  if (!make_bwd_plan(S, D, R, &stash)) return true;
+  return stash.cluster > 1 || stash.ctas_per_sm == 1;
+}
+
 }  // namespace
 }  // namespace attnres_b200
 
@@ -156,6 +166,11 @@ extern "C" const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t 
   return tma_fwd_supported(S, D, R) ? "tma" : "generic";
 }
 
+extern "C" int32_t attnres_b200_wants_output_residual(int32_t S, int32_t D, int32_t R) {
+  if (check_shape(S, 1, D, R) != ATTNRES_B200_OK) return 0;
+  return wants_output_residual(S, D, R) ? 1 : 0;
+}
+
 extern "C" int attnres_b200_error_flag(int32_t* flag, int32_t clear) {
   if (flag == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
   int value = 0;
@@ -179,12 +194,13 @@ extern "C" int attnres_b200_forward(
     int32_t S, int64_t N, int32_t D, int32_t R,
     const void* query, int64_t query_stride,
     float eps, float scale,
-    void* out, int64_t out_row_stride,
+    void* out, int64_t out_row_stride, void* out_residual,
     float* logits, float* stats,
     uint32_t flags, void* stream) {
   if (int st = check_shape(S, N, D, R)) return st;
   if (int st = check_scalars(eps, scale)) return st;
-  if (flags & ~ATTNRES_B200_FLAG_FORCE_GENERIC) return ATTNRES_B200_ERR_BAD_FLAGS;
+  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM))
+    return ATTNRES_B200_ERR_BAD_FLAGS;
   if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !out || !logits || !stats)
     return ATTNRES_B200_ERR_NULL_POINTER;
   if (!aligned2(query) || !aligned2(out)) return ATTNRES_B200_ERR_MISALIGNED;
@@ -202,9 +218,11 @@ extern "C" int attnres_b200_forward(
   p.scale = scale;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_stride = out_row_stride;
+  p.out_residual = static_cast<__nv_bfloat16*>(out_residual);
   p.logits = logits;
   p.stats = stats;
-  vec = vec && D % 8 == 0 && aligned16(out) && (N == 1 || out_row_stride % 8 == 0);
+  vec = vec && D % 8 == 0 && aligned16(out) && (N == 1 || out_row_stride % 8 == 0) &&
+        (out_residual == nullptr || aligned16(out_residual));
 
   int device = 0, sms = 0;
   if (int st = current_device(&device)) return st;
@@ -235,13 +253,15 @@ extern "C" int attnres_b200_backward(
     float eps, float scale,
     const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
     const float* logits, const float* stats,
+    const void* out_saved, const void* out_residual,
     void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
     float* dq_partials, int32_t dq_partial_rows,
     void* dq_bf16, float* dq_f32,
     uint32_t flags, void* stream) {
   if (int st = check_shape(S, N, D, R)) return st;
   if (int st = check_scalars(eps, scale)) return st;
-  if (flags & ~ATTNRES_B200_FLAG_FORCE_GENERIC) return ATTNRES_B200_ERR_BAD_FLAGS;
+  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM))
+    return ATTNRES_B200_ERR_BAD_FLAGS;
   if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !grad_out || !logits || !stats)
     return ATTNRES_B200_ERR_NULL_POINTER;
   const bool want_dq = dq_bf16 != nullptr || dq_f32 != nullptr;
@@ -282,6 +302,8 @@ extern "C" int attnres_b200_backward(
   p.go_feat_stride = go_feat_stride;
   p.logits = logits;
   p.stats = stats;
+  p.out_saved = static_cast<const __nv_bfloat16*>(out_saved);
+  p.out_residual = static_cast<const __nv_bfloat16*>(out_residual);
   p.dq_partials = want_dq ? dq_partials : nullptr;
   vec = vec && D % 8 == 0 && aligned16(grad_out) && go_feat_stride == 1 &&
         (N == 1 || go_row_stride % 8 == 0) && (!want_dq || aligned16(dq_partials));
@@ -297,8 +319,15 @@ extern "C" int attnres_b200_backward(
   int grid = max_rows;
   int st = ATTNRES_B200_ERR_CUDA;
   if (vec && !(flags & ATTNRES_B200_FLAG_FORCE_GENERIC)) {
-    // Short source lists keep the whole position in registers; longer ones stage it.
-    if (bwd_ring_supported(S, D, R)) st = launch_bwd_ring(p, sms, max_rows, &grid, cs);
+    // Short source lists keep the whole position in registers; long ones stream through a
+    // ring when the forward saved its output; the rest stage the position in shared memory.
+    const bool have_saved = out_saved != nullptr && out_residual != nullptr &&
+                            aligned16(out_saved) && aligned16(out_residual);
+    if (have_saved && bwd_stream_supported(S, D, R) &&
+        ((flags & ATTNRES_B200_FLAG_PREFER_STREAM) || wants_output_residual(S, D, R)))
+      st = launch_bwd_stream(p, sms, max_rows, &grid, cs);
+    if (st != ATTNRES_B200_OK && bwd_ring_supported(S, D, R))
+      st = launch_bwd_ring(p, sms, max_rows, &grid, cs);
     if (st != ATTNRES_B200_OK && tma_bwd_supported(S, D, R))
       st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
   }
@@ -356,6 +385,7 @@ extern "C" int attnres_b200_backward_static_scratch(
     float eps, float scale,
     const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
     const float* logits, const float* stats,
+    const void* out_saved, const void* out_residual,
     void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
     void* dq_bf16, float* dq_f32,
     uint32_t flags, void* stream) {
@@ -372,6 +402,7 @@ extern "C" int attnres_b200_backward_static_scratch(
   // stage of this same call, so stale contents from earlier calls are never read.
   return attnres_b200_backward(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query,
                                query_stride, eps, scale, grad_out, go_row_stride, go_feat_stride,
-                               logits, stats, dsrc_ptrs, dsrc_row_stride, scratch, rows, dq_bf16,
+                               logits, stats, out_saved, out_residual, dsrc_ptrs, dsrc_row_stride,
+                               scratch, rows, dq_bf16,
                                dq_f32, flags, stream);
 }

@@ -42,6 +42,9 @@ struct FwdParams {
   float scale;
   __nv_bfloat16* out;
   int64_t out_row_stride;
+  // Optional BF16 [N,D] (contiguous): the part of the FP32 result that the BF16 rounding of
+  // `out` dropped, so out + residual carries about 16 mantissa bits.  NULL skips it.
+  __nv_bfloat16* out_residual;
   float* logits;  // [S,N]
   float* stats;   // [2,N]: max, 1/denominator
 };
@@ -63,6 +66,11 @@ struct BwdParams {
   int64_t go_feat_stride;
   const float* logits;
   const float* stats;
+  // Optional: the forward's BF16 output and its residual (both [N,D] contiguous).  With them
+  // delta = sum_d dO * (out + residual) is known before any source is read, which lets the
+  // streaming backward finish every source in one pass.
+  const __nv_bfloat16* out_saved;
+  const __nv_bfloat16* out_residual;
   float* dq_partials;  // [gridDim.x, R]
 };
 

@@ -324,21 +324,22 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       p.stats[p.N + row] = inv_sum;
     }
     __nv_bfloat16* orow = p.out + row * p.out_row_stride;
+    __nv_bfloat16* rrow = p.out_residual != nullptr ? p.out_residual + row * (int64_t)D : nullptr;
     const float2 i2 = make_float2(inv_sum, inv_sum);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if (in_row[j]) {
-        uint4 packed;
-        float2 o;
-        o = __fmul2_rn(acc[j][0], i2);
-        packed.x = pack_bf16x2(o.x, o.y);
-        o = __fmul2_rn(acc[j][1], i2);
-        packed.y = pack_bf16x2(o.x, o.y);
-        o = __fmul2_rn(acc[j][2], i2);
-        packed.z = pack_bf16x2(o.x, o.y);
-        o = __fmul2_rn(acc[j][3], i2);
-        packed.w = pack_bf16x2(o.x, o.y);
-        *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = packed;
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 o = __fmul2_rn(acc[j][k], i2);
+          hi[k] = pack_bf16x2(o.x, o.y);
+          // what the BF16 rounding dropped, itself rounded to BF16
+          lo[k] = pack_bf16x2(o.x - bf16x2_lo(hi[k]), o.y - bf16x2_hi(hi[k]));
+        }
+        *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        if (rrow != nullptr)
+          *reinterpret_cast<uint4*>(rrow + (int64_t)(gl + j * L) * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
     }
   }

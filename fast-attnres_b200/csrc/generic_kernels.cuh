@@ -154,18 +154,18 @@ fwd_generic_kernel(const __grid_constant__ FwdParams p) {
       p.stats[p.N + row] = 1.0f / run_sum;
     }
     __nv_bfloat16* orow = p.out + row * p.out_row_stride;
+    __nv_bfloat16* rrow = p.out_residual != nullptr ? p.out_residual + row * (int64_t)D : nullptr;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
-      const int c = j * T + tid;
-      if constexpr (VEC == 8) {
-        if (c * 8 < D) {
-          float o[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] = acc[j * 8 + e] / run_sum;
-          *reinterpret_cast<uint4*>(orow + (int64_t)c * 8) = pack8(o);
+      for (int e = 0; e < VEC; ++e) {
+        const int d = (j * T + tid) * VEC + e;
+        if (d < D) {
+          const float o = acc[j * VEC + e] / run_sum;
+          const __nv_bfloat16 hi = __float2bfloat16_rn(o);
+          orow[d] = hi;
+          if (rrow != nullptr) rrow[d] = __float2bfloat16_rn(o - __bfloat162float(hi));
         }
-      } else {
-        if (c < D) orow[c] = __float2bfloat16_rn(acc[j] / run_sum);
       }
     }
   }

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define ATTNRES_B200_ABI_VERSION 1
+#define ATTNRES_B200_ABI_VERSION 2
 /* Envelope of the reference operator (src/attnres/_sources.py:12-13). */
 #define ATTNRES_B200_MAX_SOURCES 129
 #define ATTNRES_B200_MAX_WIDTH 8192
@@ -65,6 +65,9 @@ extern "C" {
 /* Use the layout-generic kernels even when the inputs qualify for the
  * TMA-staged fast path (used by tests to cover both families). */
 #define ATTNRES_B200_FLAG_FORCE_GENERIC 1u
+/* Backward: take the one-pass streaming kernel whenever the saved output is given and the
+ * shape allows it, whatever the library's own choice would be (tests, tuning). */
+#define ATTNRES_B200_FLAG_PREFER_STREAM 2u
 
 /* Replaces nothing in the reference; lets a binding check it loaded the
  * library it was written against. */
@@ -86,6 +89,11 @@ const char* attnres_b200_status_string(int status);
  *                      [S,N,D] tensor is passed as base + s*stride(0))
  *   query              device BF16 [R], element stride `query_stride`
  *   out                device BF16 [N,D], row stride `out_row_stride`, feature stride 1
+ *   out_residual       optional device BF16 [N,D] contiguous: what the BF16 rounding of `out`
+ *                      dropped (out + out_residual carries about 16 mantissa bits of the FP32
+ *                      result).  Ask attnres_b200_wants_output_residual whether the backward
+ *                      of this shape profits from it; NULL skips it.  The reference saves a
+ *                      full FP32 copy of the output instead (fixed_tail.py:917-919).
  *   logits             device FP32 [S,N] contiguous: scaled logits z_s
  *   stats              device FP32 [2,N] contiguous: row max, then 1/sum(exp(z-max))
  *   stream             a cudaStream_t (0 = legacy default stream)
@@ -96,9 +104,17 @@ int attnres_b200_forward(
     int32_t S, int64_t N, int32_t D, int32_t R,
     const void* query, int64_t query_stride,
     float eps, float scale,
-    void* out, int64_t out_row_stride,
+    void* out, int64_t out_row_stride, void* out_residual,
     float* logits, float* stats,
     uint32_t flags, void* stream);
+
+/*
+ * 1 when the backward of this shape (aligned layout assumed) is faster with the forward's
+ * output and residual (it then finishes every source in one pass instead of staging the
+ * whole position in shared memory), 0 otherwise.  Pure host function; plays the role of the
+ * reference's save-versus-recompute policy (fla_full_sources.py:146-161).
+ */
+int32_t attnres_b200_wants_output_residual(int32_t S, int32_t D, int32_t R);
 
 /*
  * Rows the dquery workspace must hold for a backward call of this shape on
@@ -118,6 +134,8 @@ int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t 
  *
  *   grad_out           device BF16 [N,D] with arbitrary row/feature strides
  *   logits, stats      as written by attnres_b200_forward for the same inputs
+ *   out_saved,         optional: `out` and `out_residual` of the forward (BF16 [N,D]
+ *   out_residual       contiguous).  Both or neither; NULL for both is always correct.
  *   dsrc_ptrs[s]       device BF16 [N,D] gradient of source s, row stride
  *                      dsrc_row_stride[s], feature stride 1 (host arrays, length S).
  *                      NULL skips the value gradients.
@@ -137,6 +155,7 @@ int attnres_b200_backward(
     float eps, float scale,
     const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
     const float* logits, const float* stats,
+    const void* out_saved, const void* out_residual,
     void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
     float* dq_partials, int32_t dq_partial_rows,
     void* dq_bf16, float* dq_f32,
@@ -190,6 +209,7 @@ int attnres_b200_backward_static_scratch(
     float eps, float scale,
     const void* grad_out, int64_t go_row_stride, int64_t go_feat_stride,
     const float* logits, const float* stats,
+    const void* out_saved, const void* out_residual,
     void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
     void* dq_bf16, float* dq_f32,
     uint32_t flags, void* stream);

@@ -49,7 +49,7 @@ def _forward_status(S=2, N=4, D=16, R=8, eps=2**-23, scale=1.0, src=0x1000, quer
     strides = _native.int64_array([D] * max(S, 1))
     ones = _native.int64_array([1] * max(S, 1))
     return lib.attnres_b200_forward(ptrs, strides, ones, S, N, D, R, query, 1, eps, scale,
-                                    out, D, logits, stats, flags, None)
+                                    out, D, None, logits, stats, flags, None)
 
 
 @pytest.mark.parametrize("kwargs,code", [
@@ -73,7 +73,7 @@ def test_backward_argument_errors_are_found_before_any_launch():
     def call(S=S, go=0x6000, dsrc=ptrs, dstr=strides, partials=0x7000, rows=4, dq=0x8000,
              dq32=None, eps=2**-23):
         return lib.attnres_b200_backward(ptrs, strides, ones, S, N, D, R, 0x2000, 1, eps, 1.0,
-                                         go, D, 1, 0x4000, 0x5000, dsrc, dstr, partials, rows,
+                                         go, D, 1, 0x4000, 0x5000, None, None, dsrc, dstr, partials, rows,
                                          dq, dq32, 0, None)
 
     assert call(S=0) == 2
@@ -83,6 +83,17 @@ def test_backward_argument_errors_are_found_before_any_launch():
     assert call(dstr=None) == 1
     assert call(partials=None) == 1
     assert call(dq=0x8001) == 7
+
+
+def test_output_residual_policy_is_a_pure_host_decision():
+    # short lists never want it; a position that fills an SM's shared memory does
+    assert not _native.wants_output_residual(2, 1024, 1024)
+    assert not _native.wants_output_residual(9, 2048, 2048)
+    assert _native.wants_output_residual(49, 2048, 2048)
+    assert _native.wants_output_residual(49, 4096, 4096)
+    assert _native.wants_output_residual(129, 8192, 8192)
+    assert not _native.wants_output_residual(49, 3000, 127)     # not the aligned fast class
+    assert not _native.wants_output_residual(0, 1024, 1024)
 
 
 def test_workspace_rows_validates_shape():
