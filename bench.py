@@ -205,7 +205,15 @@ class Cell:
                                   generator=generator)
         self.query = (torch.randn(width, device=device, generator=generator) * 0.02).to(torch.bfloat16)
         self.upstream = upstream
-        self.out = out_buffer[:ROWS * width].view(ROWS, width)
+        # Where the library's one-pass backward wants the forward's output and its BF16
+        # residual, both must survive until the cell's backward: such a cell owns them.
+        self.saves_output = _native.wants_output_residual(sources, width, width)
+        if self.saves_output:
+            self.out = torch.empty(ROWS, width, device=device, dtype=torch.bfloat16)
+            self.residual = torch.empty(ROWS, width, device=device, dtype=torch.bfloat16)
+        else:
+            self.out = out_buffer[:ROWS * width].view(ROWS, width)
+            self.residual = None
         self.grad = grad_buffer[:sources * ROWS * width].view(sources, ROWS, width)
         self.logits = torch.empty(sources, ROWS, device=device, dtype=torch.float32)
         self.stats = torch.empty(2, ROWS, device=device, dtype=torch.float32)
@@ -223,7 +231,8 @@ class Cell:
         from attnres import _native
         _native.forward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, self.N, self.D,
                         self.D, self.query.data_ptr(), 1, 2**-23, 1.0, self.out.data_ptr(), self.D,
-                        self.logits.data_ptr(), self.stats.data_ptr(), 0, stream)
+                        self.logits.data_ptr(), self.stats.data_ptr(), 0, stream,
+                        residual_ptr=self.residual.data_ptr() if self.saves_output else None)
 
     def backward(self, stream, distributed):
         from attnres import _native
@@ -234,7 +243,9 @@ class Cell:
                          self.grad_ptrs, [self.D] * self.S,
                          self.partials.data_ptr(), self.partial_rows,
                          None if distributed else self.dq.data_ptr(),
-                         self.dq32.data_ptr() if distributed else None, 0, stream)
+                         self.dq32.data_ptr() if distributed else None, 0, stream,
+                         out_ptr=self.out.data_ptr() if self.saves_output else None,
+                         residual_ptr=self.residual.data_ptr() if self.saves_output else None)
 
     def capture(self, distributed):
         side = torch.cuda.Stream()
@@ -361,6 +372,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "bwd_gbs": round(cell.bwd_bytes / (b * 1e-3) / 1e9, 1),
             "gbs": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9, 1),
             "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
+            "one_pass_backward": cell.saves_output,
         })
     # The CPU oracle is timed at N = 1 only (under torchrun every rank is held to one thread).
     run_cpu = not args.skip_cpu and world == 1
@@ -480,6 +492,12 @@ def run_single_cell(args) -> None:
     stream = torch.cuda.current_stream().cuda_stream
     scale = rank ** -0.5 if rank != width else 1.0
     flags = _native.FLAG_FORCE_GENERIC if args.generic else 0
+    if args.one_pass:
+        flags |= _native.FLAG_PREFER_STREAM
+    saves = args.one_pass or (not args.two_pass and
+                              _native.wants_output_residual(sources, width, rank))
+    residual = torch.empty_like(out) if saves else None
+    saved = dict(out_ptr=out.data_ptr(), residual_ptr=residual.data_ptr()) if saves else {}
     fwd_ms, bwd_ms = [], []
     for index in range(args.warmup + args.steps):
         flush.zero_()  # 256 MB write: evicts the 126 MB L2 between timed launches
@@ -487,7 +505,8 @@ def run_single_cell(args) -> None:
         e0.record()
         _native.forward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
                         query.data_ptr(), 1, 2**-23, scale, out.data_ptr(), width,
-                        logits.data_ptr(), stats.data_ptr(), flags, stream)
+                        logits.data_ptr(), stats.data_ptr(), flags, stream,
+                        residual_ptr=saved.get("residual_ptr"))
         e1.record()
         flush.zero_()
         e1b = torch.cuda.Event(enable_timing=True)
@@ -495,7 +514,8 @@ def run_single_cell(args) -> None:
         _native.backward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
                          query.data_ptr(), 1, 2**-23, scale, upstream.data_ptr(), width, 1,
                          logits.data_ptr(), stats.data_ptr(), dst, [width] * sources,
-                         partials.data_ptr(), partial_rows, dq.data_ptr(), None, flags, stream)
+                         partials.data_ptr(), partial_rows, dq.data_ptr(), None, flags, stream,
+                         **saved)
         e2.record()
         torch.cuda.synchronize()
         if index >= args.warmup:
@@ -511,7 +531,8 @@ def run_single_cell(args) -> None:
                       "family_fwd": _native.kernel_family(sources, width, rank, True, False)
                       if not args.generic else "generic",
                       "family_bwd": _native.kernel_family(sources, width, rank, True, True)
-                      if not args.generic else "generic"}), flush=True)
+                      if not args.generic else "generic",
+                      "one_pass_backward": bool(saves)}), flush=True)
 
 
 def main() -> None:
@@ -527,6 +548,10 @@ def main() -> None:
     parser.add_argument("--cell", default=None, help="S,D[,R]: time one shape instead of the sweep")
     parser.add_argument("--rows", type=int, default=ROWS, help="rows of the --cell run")
     parser.add_argument("--generic", action="store_true", help="--cell: force the generic kernels")
+    parser.add_argument("--one-pass", action="store_true",
+                        help="--cell: save the output residual and prefer the one-pass backward")
+    parser.add_argument("--two-pass", action="store_true",
+                        help="--cell: never save the output residual (staged backward)")
     args = parser.parse_args()
     if args.cell is not None:
         run_single_cell(args)

@@ -38,10 +38,22 @@ _flags = 0
 
 
 def set_kernel_flags(flags: int) -> int:
-    """Set the flag word passed to the library (0, or FLAG_FORCE_GENERIC); returns the old one."""
+    """Set the flag word passed to the library (0, FLAG_FORCE_GENERIC or FLAG_PREFER_STREAM);
+    returns the old one."""
     global _flags
     previous, _flags = _flags, int(flags)
     return previous
+
+
+def _save_residual(count: int, width: int, rank: int) -> bool:
+    """Whether the forward also writes the BF16 residual of its output.
+
+    The library's one-pass backward for long source lists needs the forward's result to
+    about 16 mantissa bits (output + residual); the decision depends on the shape only, so
+    the fake kernels below make the same one.
+    """
+    return bool(_flags & _native.FLAG_PREFER_STREAM) or \
+        _native.wants_output_residual(int(count), int(width), int(rank))
 
 
 def _rows(shape) -> int:
@@ -89,22 +101,28 @@ def _run_forward(kept, ptrs, row_strides, feat_strides, shape, query, eps, scale
     out = torch.empty(tuple(shape), device=device, dtype=torch.bfloat16)
     logits = torch.empty((S, N), device=device, dtype=torch.float32)
     stats = torch.empty((2, N), device=device, dtype=torch.float32)
+    # A 0-element residual means "not saved": the backward then takes the two-pass kernels.
+    residual = torch.empty(tuple(shape) if _save_residual(S, D, R) else (0,), device=device,
+                           dtype=torch.bfloat16)
     with torch.cuda.device(device):
         _native.forward(ptrs, row_strides, feat_strides, S, N, D, R,
                         query.data_ptr(), int(query.stride(0)), float(eps), float(scale),
                         out.data_ptr(), D, logits.data_ptr(), stats.data_ptr(),
-                        _flags, _stream(device))
+                        _flags, _stream(device),
+                        residual_ptr=residual.data_ptr() if residual.numel() else None)
     del kept
-    return out, logits, stats
+    return out, logits, stats, residual
 
 
 def _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output, logits,
-                  stats, eps, scale, grad_ptrs, need_query, query_grad_dtype=torch.bfloat16):
+                  stats, out, residual, eps, scale, grad_ptrs, need_query,
+                  query_grad_dtype=torch.bfloat16):
     S, D, R, N = len(ptrs), int(shape[-1]), int(query.numel()), _rows(shape)
     device = query.device
     upstream, go_row_stride, go_feat_stride = row_layout(grad_output.reshape(tuple(shape)))
     partials = grad_query = None
     partial_rows = 0
+    saved = residual.numel() > 0 and out.is_contiguous() and residual.is_contiguous()
     with torch.cuda.device(device):
         if need_query:
             partial_rows = _native.dq_workspace_rows(N, S, D, R, device.index)
@@ -120,7 +138,9 @@ def _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_outp
             None if partials is None else partials.data_ptr(), partial_rows,
             grad_query.data_ptr() if need_query and not as_f32 else None,
             grad_query.data_ptr() if need_query and as_f32 else None,
-            _flags, _stream(device))
+            _flags, _stream(device),
+            out_ptr=out.data_ptr() if saved else None,
+            residual_ptr=residual.data_ptr() if saved else None)
     del kept, upstream
     return grad_query
 
@@ -128,8 +148,8 @@ def _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_outp
 # --------------------------------------------------------------------------- packed
 
 @_custom_op("attnres_b200::read_packed_forward", mutates_args=(), device_types="cuda")
-def read_packed_forward(values: torch.Tensor, query: torch.Tensor, eps: float,
-                        scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def read_packed_forward(values: torch.Tensor, query: torch.Tensor, eps: float, scale: float
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     _require_cuda_bf16((values,), query)
     kept, ptrs, row_strides, feat_strides = _packed_table(values)
     return _run_forward(kept, ptrs, row_strides, feat_strides, values.shape[1:], query, eps, scale)
@@ -138,16 +158,19 @@ def read_packed_forward(values: torch.Tensor, query: torch.Tensor, eps: float,
 @read_packed_forward.register_fake
 def _(values, query, eps, scale):
     rows = _rows(values.shape[1:])
+    keep = _save_residual(values.shape[0], values.shape[-1], query.numel())
     return (values.new_empty(values.shape[1:]),
             values.new_empty((values.shape[0], rows), dtype=torch.float32),
-            values.new_empty((2, rows), dtype=torch.float32))
+            values.new_empty((2, rows), dtype=torch.float32),
+            values.new_empty(values.shape[1:] if keep else (0,)))
 
 
 @_custom_op("attnres_b200::read_packed_backward", mutates_args=(), device_types="cuda")
 def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output: torch.Tensor,
-                         logits: torch.Tensor, stats: torch.Tensor, eps: float, scale: float,
+                         logits: torch.Tensor, stats: torch.Tensor, out: torch.Tensor,
+                         residual: torch.Tensor, eps: float, scale: float,
                          need_values: bool, need_query: bool) -> tuple[torch.Tensor, torch.Tensor]:
-    _require_cuda_bf16((values, grad_output), query)
+    _require_cuda_bf16((values, grad_output, out, residual), query)
     kept, ptrs, row_strides, feat_strides = _packed_table(values)
     shape = values.shape[1:]
     count, rows, width = values.shape[0], _rows(shape), int(shape[-1])
@@ -157,7 +180,7 @@ def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output:
         step = rows * width * values.element_size()
         grad_ptrs = [grad_values.data_ptr() + s * step for s in range(count)]
     grad_query = _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output,
-                               logits, stats, eps, scale, grad_ptrs, need_query)
+                               logits, stats, out, residual, eps, scale, grad_ptrs, need_query)
     # Schema outputs are plain tensors: an unused gradient is a 0-element stand-in.
     if grad_values is None:
         grad_values = values.new_empty((0,))
@@ -167,30 +190,33 @@ def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output:
 
 
 @read_packed_backward.register_fake
-def _(values, query, grad_output, logits, stats, eps, scale, need_values, need_query):
+def _(values, query, grad_output, logits, stats, out, residual, eps, scale, need_values,
+      need_query):
     return (values.new_empty(values.shape if need_values else (0,)),
             query.new_empty(query.shape if need_query else (0,)))
 
 
 def _packed_setup(ctx, inputs, output) -> None:
     values, query, eps, scale = inputs
-    _, logits, stats = output
-    ctx.mark_non_differentiable(logits, stats)
+    out, logits, stats, residual = output
+    ctx.mark_non_differentiable(logits, stats, residual)
     ctx.set_materialize_grads(False)
-    ctx.save_for_backward(values, query, logits, stats)
+    # The output itself is kept only when its residual was written (0 elements otherwise).
+    ctx.save_for_backward(values, query, logits, stats, out if residual.numel() else residual,
+                          residual)
     ctx.eps, ctx.scale = eps, scale
 
 
-def _packed_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None):
+def _packed_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None, _grad_residual=None):
     if grad_output is None:
         return None, None, None, None
-    values, query, logits, stats = ctx.saved_tensors
+    values, query, logits, stats, out, residual = ctx.saved_tensors
     need_values, need_query = bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[1])
     if not (need_values or need_query):
         return None, None, None, None
     grad_values, grad_query = read_packed_backward(
-        values, query, grad_output, logits, stats, float(ctx.eps), float(ctx.scale),
-        need_values, need_query)
+        values, query, grad_output, logits, stats, out, residual, float(ctx.eps),
+        float(ctx.scale), need_values, need_query)
     return (grad_values if need_values else None, grad_query if need_query else None, None, None)
 
 
@@ -201,8 +227,8 @@ torch.library.register_autograd(read_packed_forward, _packed_backward, setup_con
 
 @_custom_op("attnres_b200::read_sources_forward", mutates_args=(), device_types="cuda",
             **_LIST_OP_KWARGS)
-def read_sources_forward(sources: list[torch.Tensor], query: torch.Tensor, eps: float,
-                         scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def read_sources_forward(sources: list[torch.Tensor], query: torch.Tensor, eps: float, scale: float
+                         ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     _require_cuda_bf16(sources, query)
     kept, ptrs, row_strides, feat_strides = _source_table(sources)
     return _run_forward(kept, ptrs, row_strides, feat_strides, sources[0].shape, query, eps, scale)
@@ -212,49 +238,54 @@ def read_sources_forward(sources: list[torch.Tensor], query: torch.Tensor, eps: 
 def _(sources, query, eps, scale):
     first = sources[0]
     rows = _rows(first.shape)
+    keep = _save_residual(len(sources), first.shape[-1], query.numel())
     return (first.new_empty(first.shape),
             first.new_empty((len(sources), rows), dtype=torch.float32),
-            first.new_empty((2, rows), dtype=torch.float32))
+            first.new_empty((2, rows), dtype=torch.float32),
+            first.new_empty(first.shape if keep else (0,)))
 
 
 @_custom_op("attnres_b200::read_sources_backward", mutates_args=(), device_types="cuda",
             **_LIST_OP_KWARGS)
 def read_sources_backward(sources: list[torch.Tensor], query: torch.Tensor,
                           grad_output: torch.Tensor, logits: torch.Tensor, stats: torch.Tensor,
+                          out: torch.Tensor, residual: torch.Tensor,
                           eps: float, scale: float) -> list[torch.Tensor]:
-    _require_cuda_bf16((*sources, grad_output), query)
+    _require_cuda_bf16((*sources, grad_output, out, residual), query)
     kept, ptrs, row_strides, feat_strides = _source_table(sources)
     shape = sources[0].shape
     grads = [torch.empty(tuple(shape), device=query.device, dtype=torch.bfloat16)
              for _ in sources]
     grad_query = _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output,
-                               logits, stats, eps, scale, [g.data_ptr() for g in grads], True)
+                               logits, stats, out, residual, eps, scale,
+                               [g.data_ptr() for g in grads], True)
     return [*grads, grad_query]
 
 
 @read_sources_backward.register_fake
-def _(sources, query, grad_output, logits, stats, eps, scale):
+def _(sources, query, grad_output, logits, stats, out, residual, eps, scale):
     return [source.new_empty(source.shape) for source in sources] + [query.new_empty(query.shape)]
 
 
 def _sources_setup(ctx, inputs, output) -> None:
     sources, query, eps, scale = inputs
-    _, logits, stats = output
-    ctx.mark_non_differentiable(logits, stats)
+    out, logits, stats, residual = output
+    ctx.mark_non_differentiable(logits, stats, residual)
     ctx.set_materialize_grads(False)
-    ctx.save_for_backward(*sources, query, logits, stats)
+    ctx.save_for_backward(*sources, query, logits, stats, out if residual.numel() else residual,
+                          residual)
     ctx.count = len(sources)
     ctx.eps, ctx.scale = eps, scale
 
 
-def _sources_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None):
+def _sources_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None, _grad_residual=None):
     if grad_output is None:
         return [None] * ctx.count, None, None, None
     saved = ctx.saved_tensors
     count = ctx.count
     gradients = read_sources_backward(list(saved[:count]), saved[count], grad_output,
-                                      saved[count + 1], saved[count + 2],
-                                      float(ctx.eps), float(ctx.scale))
+                                      saved[count + 1], saved[count + 2], saved[count + 3],
+                                      saved[count + 4], float(ctx.eps), float(ctx.scale))
     return gradients[:count], gradients[count], None, None
 
 

@@ -55,8 +55,10 @@ class _ShardedRead(torch.autograd.Function):
         else:
             kept, ptrs, rs, fs = _ops._source_table(sources)
             shape = sources[0].shape
-        out, logits, stats = _ops._run_forward(kept, ptrs, rs, fs, shape, query, eps, scale)
-        ctx.save_for_backward(query, logits, stats, *sources)
+        out, logits, stats, residual = _ops._run_forward(kept, ptrs, rs, fs, shape, query, eps,
+                                                         scale)
+        ctx.save_for_backward(query, logits, stats, out if residual.numel() else residual,
+                              residual, *sources)
         ctx.eps, ctx.scale, ctx.group, ctx.packed = eps, scale, group, packed
         ctx.set_materialize_grads(False)
         return out
@@ -64,10 +66,10 @@ class _ShardedRead(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         from . import _ops
-        count = len(ctx.saved_tensors) - 3
+        count = len(ctx.saved_tensors) - 5
         if grad_output is None:
             return (None,) * (5 + count)
-        query, logits, stats, *sources = ctx.saved_tensors
+        query, logits, stats, out, residual, *sources = ctx.saved_tensors
         if ctx.packed:
             values = sources[0]
             kept, ptrs, rs, fs = _ops._packed_table(values)
@@ -82,7 +84,7 @@ class _ShardedRead(torch.autograd.Function):
                      for _ in sources]
             grad_ptrs = [g.data_ptr() for g in grads]
         grad_query = _ops._run_backward(kept, ptrs, rs, fs, shape, query, grad_output, logits, stats,
-                                        ctx.eps, ctx.scale, grad_ptrs, True,
+                                        out, residual, ctx.eps, ctx.scale, grad_ptrs, True,
                                         query_grad_dtype=torch.float32)
         return (all_reduce_query_grad(grad_query, ctx.group), None, None, None, None, *grads)
 

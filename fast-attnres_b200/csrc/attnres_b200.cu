@@ -121,13 +121,28 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
 
 constexpr int kWorkspaceRowsPerSm = 8;
 
-// The streaming backward pays 6*D extra bytes per position; it wins where the staged
-// backward is held to one CTA per SM (or needs a cluster, or does not fit at all).
+// The one-pass backward moves 6*D more bytes per position (the forward writes one more BF16
+// row, the backward reads two more) and finishes each source as it arrives.  Measured on
+// B200 against the two-pass kernels (N = 16384, R = D unless noted):
+//   * it wins wherever the staged backward can hold only one position per SM, needs a
+//     cluster or does not fit (S >= 33 at D = 2048/4096, S >= 65 at D = 1024, every S at D = 8192): 1.4x to 5x;
+//   * full-width rows of 2048 and more with R = D: it wins or ties from S = 5 up
+//     (D = 4096: 5.3 vs 3.9 TB/s at S = 5, 6.3 vs 6.0 at S = 25);
+//   * D <= 1024: it wins only once the staged backward is down to two CTAs per SM (S = 49);
+//   * low-rank tails with a staged backward at two or more CTAs per SM: the two-pass kernels
+//     stay ahead by 3 to 6 %.
 bool wants_output_residual(int S, int D, int R) {
-  if (S <= 4 || !bwd_stream_supported(S, D, R)) return false;
+  BwdStreamPlan stream;
+  if (S <= 4 || !make_bwd_stream_plan(S, D, R, &stream)) return false;
   BwdPlan stash;
   if (!make_bwd_plan(S, D, R, &stash)) return true;
-  return stash.cluster > 1 || stash.ctas_per_sm == 1;
+  // One position's staged rows take more than half an SM's shared memory: the staged kernel
+  // cannot overlap two positions on an SM, whatever its CTA shape.
+  const bool one_position_per_sm = (size_t)(S + 1) * (size_t)D * 2u > 114u * 1024u;
+  if (stash.cluster > 1 || one_position_per_sm) return true;
+  const bool full_row = D / 8 == stream.group_warps * 32 * kRingChunks;
+  if (full_row && R == D && D >= 2048) return true;
+  return D <= 1024 && stash.ctas_per_sm <= 2;
 }
 
 }  // namespace

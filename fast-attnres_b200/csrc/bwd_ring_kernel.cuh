@@ -407,6 +407,8 @@ inline int launch_bwd_ring(const BwdParams& p, int sms, int max_rows, int* rows_
   const int64_t cap = (int64_t)sms * plan.ctas_per_sm;
   if (grid > cap) grid = cap;
   if (grid * groups > max_rows) grid = max_rows / groups;
+  // Fewer positions than one CTA has groups: the idle groups write no partial row.
+  if (grid < 1 && p.N <= max_rows) grid = 1;
   if (grid < 1) return 9;
   int st;
   switch (plan.group_warps) {

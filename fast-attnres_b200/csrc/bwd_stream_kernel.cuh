@@ -33,14 +33,24 @@ struct BwdStreamPlan {
   uint32_t off_bars;
   uint32_t off_part;
   uint32_t off_zl;
+  uint32_t off_tab;
   uint32_t off_abort;
   uint32_t smem_bytes;
 };
 
 constexpr int kStreamLogitSlots = 136;  // S + 2 <= 131 floats, padded
 
+// One entry of the shared-memory copy of the source table.  Indexed reads of the kernel
+// parameter block go through the small constant cache; with tens of sources they miss it on
+// the path that issues the loads, which is the path that keeps the ring full.  (The gradient
+// table stays in the parameter block: its reads are hoisted far ahead of the stores, and a
+// shared-memory copy measured slower.)
+struct __align__(16) StreamRowRef {
+  uint64_t base;       // address of row 0
+  int64_t row_stride;  // elements
+};
+
 inline bool make_bwd_stream_plan(int S, int D, int R, BwdStreamPlan* plan) {
-  (void)S;
   if (!tma_shape_ok(D, R)) return false;
   const int chunks = D / 8;
   const int need = (chunks + 32 * kRingChunks - 1) / (32 * kRingChunks);
@@ -56,7 +66,8 @@ inline bool make_bwd_stream_plan(int S, int D, int R, BwdStreamPlan* plan) {
   const uint32_t bars = (uint32_t)groups * 8u * 8u;
   const uint32_t part = (uint32_t)groups * 2u * kRingMaxGroupWarps * 16u;
   const uint32_t zl = (uint32_t)groups * 3u * kStreamLogitSlots * 4u;
-  const uint32_t fixed = bars + part + zl + 16u + 128u;
+  const uint32_t tab = (uint32_t)S * (uint32_t)sizeof(StreamRowRef);
+  const uint32_t fixed = bars + part + zl + tab + 16u + 128u;
   const uint32_t room = (228u * 1024u - (uint32_t)p.ctas_per_sm * 1024u) / (uint32_t)p.ctas_per_sm;
   const uint32_t usable = room < (uint32_t)kSmemPerCtaMax ? room : (uint32_t)kSmemPerCtaMax;
   int stages = usable > fixed ? (int)((usable - fixed) / ((uint32_t)groups * row_bytes)) : 0;
@@ -70,6 +81,8 @@ inline bool make_bwd_stream_plan(int S, int D, int R, BwdStreamPlan* plan) {
   off = p.off_part + part;
   p.off_zl = off;
   off += zl;
+  p.off_tab = align_up(off, 16);
+  off = p.off_tab + tab;
   p.off_abort = off;
   off += 16;
   p.smem_bytes = off;
@@ -90,9 +103,16 @@ __device__ __forceinline__ void unpack_pairs(const uint4& raw, float2* f) {
   f[3] = make_float2(bf16x2_lo(raw.w), bf16x2_hi(raw.w));
 }
 
-template <int G>
+// FULL: the row is exactly G*32*4 chunks wide, so no lane ever holds a chunk beyond the row.
+// TAIL0 >= 0 (needs FULL): the query tail starts at a lane-group boundary, chunks j >= TAIL0
+// of every lane are tail chunks; TAIL0 < 0: per-lane predicates decide.
+// SR (needs FULL): row size and ring depth (eight stages) are compile-time constants.
+// ZE: registers of an absent second source are zero-filled (only changes code placement).
+template <int G, bool FULL, int TAIL0, bool SR, bool ZE>
 __global__ void __launch_bounds__((G > 4 ? 8 : 4) * 32, G > 4 ? 1 : 3)
 bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdStreamPlan plan) {
+  static_assert(TAIL0 < 0 || FULL, "a compile-time tail boundary needs a full row");
+  static_assert(!SR || FULL, "compile-time ring constants need a full row");
   constexpr int NV = kRingChunks, B = 2;
   constexpr int WARPS = G > 4 ? 8 : 4;
   constexpr int GROUPS = WARPS / G;
@@ -101,8 +121,11 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp / G, wig = warp % G;
   const int gl = wig * 32 + lane;
-  const int S = p.S, D = p.D, R = p.R;
-  const int CH = D / 8, c0 = (D - R) / 8, nst = plan.stages;
+  const int S = p.S, R = p.R;
+  // Full-row instances: width, row size and ring depth are compile-time constants.
+  const int D = SR ? L * NV * 8 : p.D;
+  const int CH = D / 8, c0 = (D - R) / 8;
+  const int nst = SR ? kRingStaticStages : plan.stages;
   const int items = S + 3;  // dO, out, residual, then the sources
   const uint32_t row_bytes = (uint32_t)D * 2u;
   unsigned char* ring = smem + (size_t)group * (size_t)nst * row_bytes;
@@ -111,7 +134,12 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
                     group * (2 * kRingMaxGroupWarps);  // [2][8] x (ss0, dw0, ss1, dw1)
   float* zl_sm = reinterpret_cast<float*>(smem + plan.off_zl) + group * (3 * kStreamLogitSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + plan.off_abort);
+  StreamRowRef* src_tab = reinterpret_cast<StreamRowRef*>(smem + plan.off_tab);
 
+  for (int s = tid; s < S; s += WARPS * 32) {
+    src_tab[s].base = reinterpret_cast<uint64_t>(p.src.ptr[s]);
+    src_tab[s].row_stride = p.src.row_stride[s];
+  }
   if (tid == 0) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + plan.off_bars);
     for (int g = 0; g < GROUPS; ++g)
@@ -121,17 +149,24 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   }
   __syncthreads();
 
-  bool in_row[NV], in_tail[NV];
+  bool in_row_rt[NV], in_tail_rt[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = gl + j * L;
+    in_row_rt[j] = c < CH;
+    in_tail_rt[j] = in_row_rt[j] && c >= c0;
+  }
+  // With compile-time j these fold to constants in the specialised instances.
+  auto row_ok = [&](int j) { return FULL ? true : in_row_rt[j]; };
+  auto tail_ok = [&](int j) { return TAIL0 >= 0 ? j >= TAIL0 : in_tail_rt[j]; };
   float2 q2[NV][4], dq2[NV][4];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int c = gl + j * L;
-    in_row[j] = c < CH;
-    in_tail[j] = in_row[j] && c >= c0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo = 0.f, hi = 0.f;
-      if (in_tail[j]) {
+      if (tail_ok(j)) {
         const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
         lo = __bfloat162float(p.query[r * p.query_stride]);
         hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
@@ -154,7 +189,10 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
     if (issue_item == 0) src = p.grad_out + issue_row * p.go_row_stride;
     else if (issue_item == 1) src = p.out_saved + issue_row * (int64_t)D;
     else if (issue_item == 2) src = p.out_residual + issue_row * (int64_t)D;
-    else src = p.src.ptr[issue_item - 3] + issue_row * p.src.row_stride[issue_item - 3];
+    else {
+      const StreamRowRef ref = src_tab[issue_item - 3];
+      src = reinterpret_cast<const __nv_bfloat16*>(ref.base) + issue_row * ref.row_stride;
+    }
     mbar_expect_tx(&full_bar[issue_stage], row_bytes);
     bulk_load(ring + (uint32_t)issue_stage * row_bytes, src, row_bytes, &full_bar[issue_stage]);
     ++in_flight;
@@ -185,26 +223,9 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   };
   if (my_rows > 0) stage_logits(gid, 0);
 
-  int use_stage = 0;
-  uint32_t use_phase = 0;
+  RingCursor<SR> cursor(nst);
   int buf = 0, zbuf = 0;
   const float inv_rank = 1.0f / (float)R;
-  auto stage_of = [&](int ahead, uint32_t& phase) {
-    int stage = use_stage + ahead;
-    phase = use_phase;
-    if (stage >= nst) {
-      stage -= nst;
-      phase ^= 1u;
-    }
-    return stage;
-  };
-  auto consume = [&](int count) {
-    use_stage += count;
-    if (use_stage >= nst) {
-      use_stage -= nst;
-      use_phase ^= 1u;
-    }
-  };
 
   for (int64_t row = gid; row < p.N; row += total_groups, zbuf = zbuf == 2 ? 0 : zbuf + 1) {
     if (row + total_groups < p.N) {
@@ -219,11 +240,11 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
     float delta;
     {
       uint32_t phase;
-      const int sg = stage_of(0, phase);
+      const int sg = cursor.stage(0, &phase);
       mbar_wait_fast(&full_bar[sg], phase, abort_flag);
-      const int so = stage_of(1, phase);
+      const int so = cursor.stage(1, &phase);
       mbar_wait_fast(&full_bar[so], phase, abort_flag);
-      const int sr = stage_of(2, phase);
+      const int sr = cursor.stage(2, &phase);
       mbar_wait_fast(&full_bar[sr], phase, abort_flag);
       const uint4* gp = reinterpret_cast<const uint4*>(ring + (uint32_t)sg * row_bytes) + gl;
       const uint4* op = reinterpret_cast<const uint4*>(ring + (uint32_t)so * row_bytes) + gl;
@@ -231,7 +252,7 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
       float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
       for (int j = 0; j < NV; ++j) {
-        if (in_row[j]) {
+        if (row_ok(j)) {
           unpack_pairs(gp[j * L], g2[j]);
           float2 o[4], r[4];
           unpack_pairs(op[j * L], o);
@@ -262,39 +283,41 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
         in_flight -= 3;
         while (rows_to_issue > 0 && in_flight < nst) issue_one();
       }
-      consume(3);
+      cursor.advance(3);
     }
     const float* zl = zl_sm + zbuf * kStreamLogitSlots;
     if (G == 1) __syncwarp();
     const float row_max = zl[S], inv_sum = zl[S + 1];
 
-    // ---- the sources, two at a time
-    for (int s0 = 0; s0 < S; s0 += B, buf ^= 1) {
-      const int nb = (S - s0) < B ? (S - s0) : B;
+    // ---- the sources, two at a time (and a last single one when S is odd)
+    // (A compile-time source count per batch lets the compiler interleave both sources and
+    // spill; the count stays a run-time value here.)
+    auto batch = [&](const int NB, const int s0) {
       uint4 raw[B][NV];
       float part[2 * B];
 #pragma unroll
       for (int b = 0; b < B; ++b) {
         float2 ss2 = make_float2(0.f, 0.f), dw2 = make_float2(0.f, 0.f);
-        if (b < nb) {
+        if (b < NB) {
+          uint4(&mine)[NV] = raw[b];
           uint32_t phase;
-          const int stage = stage_of(b, phase);
+          const int stage = cursor.stage(b, &phase);
           mbar_wait_fast(&full_bar[stage], phase, abort_flag);
           const uint4* vrow = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
 #pragma unroll
-          for (int j = 0; j < NV; ++j) raw[b][j] = in_row[j] ? vrow[j * L] : make_uint4(0u, 0u, 0u, 0u);
+          for (int j = 0; j < NV; ++j) mine[j] = row_ok(j) ? vrow[j * L] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int j = 0; j < NV; ++j) {
             float2 v[4];
-            unpack_pairs(raw[b][j], v);
+            unpack_pairs(mine[j], v);
 #pragma unroll
             for (int k = 0; k < 4; ++k) dw2 = __ffma2_rn(v[k], g2[j][k], dw2);
-            if (in_tail[j]) {
+            if (tail_ok(j)) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) ss2 = __ffma2_rn(v[k], v[k], ss2);
             }
           }
-        } else {
+        } else if (ZE) {
 #pragma unroll
           for (int j = 0; j < NV; ++j) raw[b][j] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -334,59 +357,60 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
       }
       if (leader) {
         fence_proxy_async();
-        in_flight -= nb;
+        in_flight -= NB;
         while (rows_to_issue > 0 && in_flight < nst) issue_one();
       }
-      consume(nb);
+      cursor.advance(NB);
 
-      // ---- finish both sources from the chunks still in registers
+      // ---- finish the batch from the chunks still in registers
 #pragma unroll
       for (int b = 0; b < B; ++b) {
-        if (b < nb) {
-          const int s = s0 + b;
-          const float z = zl[s];
-          const float prob = __expf(z - row_max) * inv_sum;
-          const float ir = rsqrtf(tot[2 * b] * inv_rank + p.eps);
-          const float dz = prob * (tot[2 * b + 1] - delta);
-          const float ca = ir * p.scale * dz, cb = ir * ir * dz * z * inv_rank;
-          const float2 ps2 = make_float2(prob, prob), ca2 = make_float2(ca, ca),
-                       ncb2 = make_float2(-cb, -cb);
-          __nv_bfloat16* out_row = p.write_dv ? p.grad.ptr[s] + row * p.grad.row_stride[s] : nullptr;
+        if (b >= NB) break;
+        const int s = s0 + b;
+        const float z = zl[s];
+        const float prob = __expf(z - row_max) * inv_sum;
+        const float ir = rsqrtf(tot[2 * b] * inv_rank + p.eps);
+        const float dz = prob * (tot[2 * b + 1] - delta);
+        const float ca = ir * p.scale * dz, cb = ir * ir * dz * z * inv_rank;
+        const float2 ps2 = make_float2(prob, prob), ca2 = make_float2(ca, ca),
+                     ncb2 = make_float2(-cb, -cb);
+        __nv_bfloat16* out_row = p.write_dv ? p.grad.ptr[s] + row * p.grad.row_stride[s] : nullptr;
 #pragma unroll
-          for (int j = 0; j < NV; ++j) {
-            if (in_row[j]) {
-              float2 dv[4];
+        for (int j = 0; j < NV; ++j) {
+          if (row_ok(j)) {
+            float2 dv[4];
 #pragma unroll
-              for (int k = 0; k < 4; ++k) dv[k] = __fmul2_rn(ps2, g2[j][k]);
-              if (in_tail[j]) {
-                float2 v[4];
-                unpack_pairs(raw[b][j], v);
+            for (int k = 0; k < 4; ++k) dv[k] = __fmul2_rn(ps2, g2[j][k]);
+            if (tail_ok(j)) {
+              float2 v[4];
+              unpack_pairs(raw[b][j], v);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  dv[k] = __ffma2_rn(ncb2, v[k], __ffma2_rn(ca2, q2[j][k], dv[k]));
-                  dq2[j][k] = __ffma2_rn(ca2, v[k], dq2[j][k]);
-                }
+              for (int k = 0; k < 4; ++k) {
+                dv[k] = __ffma2_rn(ncb2, v[k], __ffma2_rn(ca2, q2[j][k], dv[k]));
+                dq2[j][k] = __ffma2_rn(ca2, v[k], dq2[j][k]);
               }
-              if (out_row != nullptr) {
-                uint4 packed;
-                packed.x = pack_bf16x2(dv[0].x, dv[0].y);
-                packed.y = pack_bf16x2(dv[1].x, dv[1].y);
-                packed.z = pack_bf16x2(dv[2].x, dv[2].y);
-                packed.w = pack_bf16x2(dv[3].x, dv[3].y);
-                *reinterpret_cast<uint4*>(out_row + (int64_t)(gl + j * L) * 8) = packed;
-              }
+            }
+            if (out_row != nullptr) {
+              uint4 packed;
+              packed.x = pack_bf16x2(dv[0].x, dv[0].y);
+              packed.y = pack_bf16x2(dv[1].x, dv[1].y);
+              packed.z = pack_bf16x2(dv[2].x, dv[2].y);
+              packed.w = pack_bf16x2(dv[3].x, dv[3].y);
+              *reinterpret_cast<uint4*>(out_row + (int64_t)(gl + j * L) * 8) = packed;
             }
           }
         }
       }
-    }
+      buf ^= 1;
+    };
+    for (int s0 = 0; s0 < S; s0 += B) batch(S - s0 < B ? S - s0 : B, s0);
   }
 
   if (p.dq_partials != nullptr && gid < p.N) {
     float* prow = p.dq_partials + gid * R;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-      if (in_tail[j]) {
+      if (tail_ok(j)) {
         float4* dst = reinterpret_cast<float4*>(prow + (int64_t)(gl + j * L - c0) * 8);
         dst[0] = make_float4(dq2[j][0].x, dq2[j][0].y, dq2[j][1].x, dq2[j][1].y);
         dst[1] = make_float4(dq2[j][2].x, dq2[j][2].y, dq2[j][3].x, dq2[j][3].y);
@@ -400,12 +424,29 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   }
 }
 
+template <int G, bool FULL, int TAIL0, bool SR, bool ZE>
+inline int launch_bwd_stream_variant(const BwdParams& p, const BwdStreamPlan& plan, int grid,
+                                     cudaStream_t stream) {
+  auto kernel = bwd_stream_kernel<G, FULL, TAIL0, SR, ZE>;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
+  return cudaGetLastError() == cudaSuccess ? 0 : 9;
+}
+
+// Which switches win was measured per group size on B200 (N = 16384, S = 9..97, GB/s of
+// algorithmic bytes at S = 49, best against worst combination):
+//   G = 1 (D = 1024): all three on, 5141 against 3484;   G = 2 (D = 2048): SR + ZE, 6186 / 5375;
+//   G = 4 (D = 4096): none, 6336 / 5393 (SR alone costs 14 %);   G = 8 (D = 8192): SR + tail, 6342 / 5489.
 template <int G>
 inline int launch_bwd_stream_instance(const BwdParams& p, const BwdStreamPlan& plan, int grid,
                                       cudaStream_t stream) {
-  if (int st = prepare_kernel(bwd_stream_kernel<G>, plan.smem_bytes)) return st;
-  bwd_stream_kernel<G><<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
-  return cudaGetLastError() == cudaSuccess ? 0 : 9;
+  const bool full = p.D / 8 == G * 32 * kRingChunks && plan.stages == kRingStaticStages;
+  if (!full) return launch_bwd_stream_variant<G, false, -1, false, false>(p, plan, grid, stream);
+  constexpr bool SR = G != 4, ZE = G <= 2;
+  constexpr int TAIL0 = (G == 1 || G == 8) ? 0 : -1;
+  if (TAIL0 == 0 && p.R == p.D)
+    return launch_bwd_stream_variant<G, true, TAIL0, SR, ZE>(p, plan, grid, stream);
+  return launch_bwd_stream_variant<G, true, -1, SR, ZE>(p, plan, grid, stream);
 }
 
 // `max_rows` bounds the dquery partial rows (one per group); the count used is returned.
@@ -418,6 +459,8 @@ inline int launch_bwd_stream(const BwdParams& p, int sms, int max_rows, int* row
   const int64_t cap = (int64_t)sms * plan.ctas_per_sm;
   if (grid > cap) grid = cap;
   if (grid * groups > max_rows) grid = max_rows / groups;
+  // Fewer positions than one CTA has groups: the idle groups write no partial row.
+  if (grid < 1 && p.N <= max_rows) grid = 1;
   if (grid < 1) return 9;
   int st;
   switch (plan.group_warps) {

@@ -18,9 +18,16 @@
 // The kernel is specialised at compile time on G and on TAIL0, the first of the
 // lane's four chunks that lies in the tail key when the boundary D-R falls on a
 // multiple of the group width (TAIL0 = 0 is R = D; D = 4096 with R = 1024 is
-// TAIL0 = 3), so the common shapes run without per-chunk predicates.  TAIL0 = -1
-// is the predicated form for every other aligned shape.
+// TAIL0 = 3), so the common shapes run without per-chunk predicates; those
+// instances can also take the row size and the ring depth (eight stages) as
+// compile-time constants (template parameter SR), which turns the ring addressing
+// into shifts and masks.  TAIL0 = -1 is the
+// predicated form for every other aligned shape.  The batch body is instantiated
+// for two sources and, for an odd source count, once more for the last one, so no
+// per-source "is this source present" test runs in the loop.
 #pragma once
+
+#include <type_traits>
 
 #include "tma_common.cuh"
 
@@ -29,6 +36,43 @@ namespace attnres_b200 {
 constexpr int kRingChunks = 4;  // 16-byte chunks per lane
 constexpr int kRingBatch = 2;   // sources folded per reduction
 constexpr int kRingMaxGroupWarps = 8;
+constexpr int kRingStaticStages = 8;  // ring depth of the specialised instances
+
+// The next item to consume in a group's ring.  With a compile-time depth of eight stages
+// the stage is the low three bits of a running counter and the mbarrier phase the bit
+// above them; otherwise stage and phase advance incrementally (no division either way).
+template <bool STATIC>
+struct RingCursor {
+  int at = 0;          // STATIC: item counter modulo 16; otherwise the stage index
+  uint32_t phase = 0;  // used by the dynamic form only
+  int depth;
+  __device__ __forceinline__ explicit RingCursor(int stages) : depth(stages) {}
+  __device__ __forceinline__ int stage(int ahead, uint32_t* parity) const {
+    if (STATIC) {
+      const uint32_t item = (uint32_t)(at + ahead);
+      *parity = (item >> 3) & 1u;
+      return (int)(item & 7u);
+    }
+    int st = at + ahead;
+    *parity = phase;
+    if (st >= depth) {
+      st -= depth;
+      *parity ^= 1u;
+    }
+    return st;
+  }
+  __device__ __forceinline__ void advance(int count) {
+    if (STATIC) {
+      at = (at + count) & 15;
+    } else {
+      at += count;
+      if (at >= depth) {
+        at -= depth;
+        phase ^= 1u;
+      }
+    }
+  }
+};
 
 struct FwdRingPlan {
   int group_warps;  // G
@@ -55,7 +99,6 @@ inline bool make_fwd_plan(int S, int D, int R, FwdRingPlan* plan) {
   p.cta_warps = G > 4 ? 8 : 4;
   p.ctas_per_sm = p.cta_warps == 4 ? 3 : 1;
   const int lanes = 32 * G, c0 = (D - R) / 8;
-  p.tail0 = (chunks == lanes * kRingChunks && c0 % lanes == 0) ? c0 / lanes : -1;
   const int groups = p.cta_warps / G;
   const uint32_t row_bytes = (uint32_t)D * 2u;
   const uint32_t fixed = 4u * 8u * 8u + 4u * 2u * 2u * kRingBatch * kRingMaxGroupWarps * 4u + 16u + 1024u;
@@ -64,6 +107,9 @@ inline bool make_fwd_plan(int S, int D, int R, FwdRingPlan* plan) {
   if (stages > 8) stages = 8;
   if (stages < 4) return false;
   p.stages = stages;
+  // The specialised instances assume a full row and a ring of exactly eight stages.
+  p.tail0 = (chunks == lanes * kRingChunks && c0 % lanes == 0 && stages == kRingStaticStages)
+                ? c0 / lanes : -1;
   uint32_t off = (uint32_t)groups * (uint32_t)stages * row_bytes;
   p.off_bars = align_up(off, 8);
   off = p.off_bars + (uint32_t)groups * (uint32_t)stages * 8u;
@@ -100,7 +146,7 @@ __device__ __forceinline__ void mbar_wait_fast(uint64_t* bar, uint32_t parity,
   if (!mbar_try_wait(bar, parity)) mbar_wait_slow(bar, parity, abort_flag);
 }
 
-template <int G, int TAIL0>
+template <int G, int TAIL0, bool SR>
 __global__ void __launch_bounds__((G > 4 ? 8 : 4) * 32, G > 4 ? 1 : 3)
 fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ FwdRingPlan plan) {
   constexpr int NV = kRingChunks, B = kRingBatch;
@@ -108,13 +154,17 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   constexpr int GROUPS = WARPS / G;
   constexpr int L = G * 32;
   constexpr bool STATIC_TAIL = TAIL0 >= 0;
+  static_assert(!SR || STATIC_TAIL, "compile-time ring constants need a full row");
   static_assert(B == 2, "the folded reduction below is written for two sources per batch");
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp / G, wig = warp % G;
   const int gl = wig * 32 + lane;
-  const int S = p.S, D = p.D, R = p.R;
-  const int CH = D / 8, c0 = (D - R) / 8, nst = plan.stages;
+  const int S = p.S, R = p.R;
+  // Full-row instances: width, row size and ring depth are compile-time constants.
+  const int D = SR ? L * NV * 8 : p.D;
+  const int CH = D / 8, c0 = (D - R) / 8;
+  const int nst = SR ? kRingStaticStages : plan.stages;
   const uint32_t row_bytes = (uint32_t)D * 2u;
   unsigned char* ring = smem + (size_t)group * (size_t)nst * row_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + plan.off_bars) + group * nst;
@@ -155,8 +205,7 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   const int64_t my_rows = gid < p.N ? (p.N - gid + total_groups - 1) / total_groups : 0;
   const bool leader = gl == 0;
 
-  // Leader's issue cursor: items are (row, source) pairs in consumption order.  Stage
-  // indices and phase bits advance incrementally (no division on the hot path).
+  // Leader's issue cursor: items are (row, source) pairs in consumption order.
   int64_t rows_to_issue = my_rows;  // rows with at least one source not yet requested
   int in_flight = 0;                // requested, not yet consumed
   int issue_stage = 0;
@@ -179,8 +228,7 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     while (rows_to_issue > 0 && in_flight < nst) issue_one();
   }
 
-  int use_stage = 0;
-  uint32_t use_phase = 0;  // stage and phase bit of the next item to consume
+  RingCursor<SR> cursor(nst);
   int buf = 0;
   const float inv_rank = 1.0f / (float)R;
   for (int64_t row = gid; row < p.N; row += total_groups) {
@@ -191,20 +239,17 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       for (int k = 0; k < 4; ++k) acc[j][k] = make_float2(0.f, 0.f);
     float run_max = -INFINITY, run_sum = 0.f;
 
-    for (int s0 = 0; s0 < S; s0 += B, buf ^= 1) {
-      const int nb = (S - s0) < B ? (S - s0) : B;
-      float2 v2[B][NV][4];
+    // One batch of NB (1 or 2) sources starting at source s0.
+    auto batch = [&](auto nb_tag, const int s0) {
+      constexpr int NB = decltype(nb_tag)::value;
+      float2 v2[NB][NV][4];
       float part[2 * B];
 #pragma unroll
       for (int b = 0; b < B; ++b) {
         float2 ss2 = make_float2(0.f, 0.f), dt2 = make_float2(0.f, 0.f);
-        if (b < nb) {
-          int stage = use_stage + b;
-          uint32_t phase = use_phase;
-          if (stage >= nst) {
-            stage -= nst;
-            phase ^= 1u;
-          }
+        if (b < NB) {
+          uint32_t phase;
+          const int stage = cursor.stage(b, &phase);
           mbar_wait_fast(&full_bar[stage], phase, abort_flag);
           const uint4* vrow = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
           uint4 raw[NV];
@@ -215,23 +260,19 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
           }
 #pragma unroll
           for (int j = 0; j < NV; ++j) {
-            v2[b][j][0] = make_float2(bf16x2_lo(raw[j].x), bf16x2_hi(raw[j].x));
-            v2[b][j][1] = make_float2(bf16x2_lo(raw[j].y), bf16x2_hi(raw[j].y));
-            v2[b][j][2] = make_float2(bf16x2_lo(raw[j].z), bf16x2_hi(raw[j].z));
-            v2[b][j][3] = make_float2(bf16x2_lo(raw[j].w), bf16x2_hi(raw[j].w));
+            float2(&v)[4] = v2[b < NB ? b : 0][j];
+            v[0] = make_float2(bf16x2_lo(raw[j].x), bf16x2_hi(raw[j].x));
+            v[1] = make_float2(bf16x2_lo(raw[j].y), bf16x2_hi(raw[j].y));
+            v[2] = make_float2(bf16x2_lo(raw[j].z), bf16x2_hi(raw[j].z));
+            v[3] = make_float2(bf16x2_lo(raw[j].w), bf16x2_hi(raw[j].w));
             if (in_tail[j]) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                ss2 = __ffma2_rn(v2[b][j][k], v2[b][j][k], ss2);
-                dt2 = __ffma2_rn(v2[b][j][k], q2[j][k], dt2);
+                ss2 = __ffma2_rn(v[k], v[k], ss2);
+                dt2 = __ffma2_rn(v[k], q2[j][k], dt2);
               }
             }
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < NV; ++j)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) v2[b][j][k] = make_float2(0.f, 0.f);
         }
         part[2 * b] = ss2.x + ss2.y;
         part[2 * b + 1] = dt2.x + dt2.y;
@@ -272,21 +313,18 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
       // Every lane of the group has read its chunks of these stages: refill them.
       if (leader) {
         fence_proxy_async();
-        in_flight -= nb;
+        in_flight -= NB;
         while (rows_to_issue > 0 && in_flight < nst) issue_one();
       }
 
       // Online softmax over the batch.
-      float z[B];
+      float z[NB];
       float new_max = run_max;
 #pragma unroll
-      for (int b = 0; b < B; ++b) {
-        z[b] = -INFINITY;
-        if (b < nb) {
-          const float inv_rms = rsqrtf(tot[2 * b] * inv_rank + p.eps);
-          z[b] = tot[2 * b + 1] * inv_rms * p.scale;
-          new_max = fmaxf(new_max, z[b]);
-        }
+      for (int b = 0; b < NB; ++b) {
+        const float inv_rms = rsqrtf(tot[2 * b] * inv_rank + p.eps);
+        z[b] = tot[2 * b + 1] * inv_rms * p.scale;
+        new_max = fmaxf(new_max, z[b]);
       }
       if (new_max != run_max) {
         const float rescale = __expf(run_max - new_max);
@@ -299,24 +337,22 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
         run_max = new_max;
       }
 #pragma unroll
-      for (int b = 0; b < B; ++b) {
-        if (b < nb) {
-          const float w = __expf(z[b] - new_max);
-          run_sum += w;
-          const float2 w2 = make_float2(w, w);
+      for (int b = 0; b < NB; ++b) {
+        const float w = __expf(z[b] - new_max);
+        run_sum += w;
+        const float2 w2 = make_float2(w, w);
 #pragma unroll
-          for (int j = 0; j < NV; ++j)
+        for (int j = 0; j < NV; ++j)
 #pragma unroll
-            for (int k = 0; k < 4; ++k) acc[j][k] = __ffma2_rn(w2, v2[b][j][k], acc[j][k]);
-          if (leader) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
-        }
+          for (int k = 0; k < 4; ++k) acc[j][k] = __ffma2_rn(w2, v2[b][j][k], acc[j][k]);
+        if (leader) p.logits[(int64_t)(s0 + b) * p.N + row] = z[b];
       }
-      use_stage += nb;
-      if (use_stage >= nst) {
-        use_stage -= nst;
-        use_phase ^= 1u;
-      }
-    }
+      cursor.advance(NB);
+      buf ^= 1;
+    };
+    int s0 = 0;
+    for (; s0 + B <= S; s0 += B) batch(std::integral_constant<int, B>{}, s0);
+    if (s0 < S) batch(std::integral_constant<int, 1>{}, s0);
 
     const float inv_sum = 1.0f / run_sum;
     if (leader) {
@@ -352,11 +388,15 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   }
 }
 
+// Compile-time ring constants measured 1 % faster for eight-warp groups (D = 8192) and 1 to
+// 7 % slower for the narrower ones (D = 4096: 5.9 against 6.4 TB/s at S = 49), so only the
+// eight-warp instances use them.
 template <int G, int TAIL0>
 inline int launch_fwd_ring(const FwdParams& p, const FwdRingPlan& plan, int grid,
                            cudaStream_t stream) {
-  if (int st = prepare_kernel(fwd_ring_kernel<G, TAIL0>, plan.smem_bytes)) return st;
-  fwd_ring_kernel<G, TAIL0><<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
+  auto kernel = fwd_ring_kernel<G, TAIL0, (G == 8 && TAIL0 >= 0)>;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }
 

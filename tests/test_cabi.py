@@ -86,9 +86,14 @@ def test_backward_argument_errors_are_found_before_any_launch():
 
 
 def test_output_residual_policy_is_a_pure_host_decision():
-    # short lists never want it; a position that fills an SM's shared memory does
+    # lists of up to four sources never want it; a position that fills an SM's shared
+    # memory does, and so do full-width rows of 2048 and more with a full-rank query
     assert not _native.wants_output_residual(2, 1024, 1024)
-    assert not _native.wants_output_residual(9, 2048, 2048)
+    assert not _native.wants_output_residual(4, 4096, 4096)
+    assert not _native.wants_output_residual(25, 1024, 1024)
+    assert not _native.wants_output_residual(7, 4096, 1024)
+    assert _native.wants_output_residual(9, 2048, 2048)
+    assert _native.wants_output_residual(49, 1024, 1024)
     assert _native.wants_output_residual(49, 2048, 2048)
     assert _native.wants_output_residual(49, 4096, 4096)
     assert _native.wants_output_residual(129, 8192, 8192)

@@ -23,12 +23,15 @@ GOLDEN = np.load(Path(__file__).parent / "golden" / "reference_oracle.npz")
 BF16 = torch.bfloat16
 
 
-@pytest.fixture(params=["auto", "generic"])
+@pytest.fixture(params=["auto", "generic", "stream"])
 def family(request):
-    """Run a test once with the library's own kernel choice and once forced onto the
-    layout-generic kernels."""
+    """Run a test with the library's own kernel choice, forced onto the layout-generic
+    kernels, and with the forward saving its output residual for the one-pass backward
+    wherever that kernel supports the shape (elsewhere the residual is written and unused)."""
     from attnres import _native, _ops
-    previous = _ops.set_kernel_flags(_native.FLAG_FORCE_GENERIC if request.param == "generic" else 0)
+    flags = {"auto": 0, "generic": _native.FLAG_FORCE_GENERIC,
+             "stream": _native.FLAG_PREFER_STREAM}[request.param]
+    previous = _ops.set_kernel_flags(flags)
     yield request.param
     _ops.set_kernel_flags(previous)
 
@@ -453,7 +456,7 @@ def test_routing_regimes_with_graph_replay(kind, rows, width, rank, family):
                 # reference's list kernel does, src/attnres/_kernels/fla_full_sources.py:389-394)
                 # give visibly different weights.  Hold the kernel's saved logits to 4 ulp of
                 # the float64 value and everything downstream to the closed form GIVEN them.
-                _, logits, _ = torch.ops.attnres_b200.read_sources_forward(
+                _, logits, _, _ = torch.ops.attnres_b200.read_sources_forward(
                     list(values.detach().unbind()), query.detach(), float(eps), float(scale))
                 v64 = values.detach().double().cpu().numpy()
                 q64 = query.detach().double().cpu().numpy()
@@ -552,7 +555,8 @@ def test_learned_query_module_on_device(family):
 # ------------------------------------------------------------------ torch.compile / CUDA graphs
 
 @pytest.mark.parametrize("shape", [(9, 65, 256, 32), (9, 65, 1024, 512), (33, 19, 2047, 1024),
-                                   (5, 48, 2048, 2048)], ids=lambda s: "x".join(map(str, s)))
+                                   (5, 48, 2048, 2048), (49, 40, 2048, 2048)],
+                         ids=lambda s: "x".join(map(str, s)))
 def test_compiled_fullgraph_and_raw_graph_replay(shape):
     """torch.compile(fullgraph=True, dynamic=False) forward+backward, then a raw CUDA graph
     of the eager ops replayed with 8 changed inputs (validation/gpu_checks.py:77-132)."""
@@ -660,8 +664,9 @@ def test_compiled_source_list_never_packs_and_does_not_recompile():
 
 # ------------------------------------------------------------------ raw C ABI
 
-@pytest.mark.parametrize("flags", [0, 1])
-@pytest.mark.parametrize("shape", [(5, 37, 1024, 1024), (3, 11, 200, 72), (4, 9, 2048, 512)])
+@pytest.mark.parametrize("flags", [0, 1, 2])
+@pytest.mark.parametrize("shape", [(5, 37, 1024, 1024), (3, 11, 200, 72), (4, 9, 2048, 512),
+                                   (7, 21, 4096, 1024)])
 def test_c_abi_direct_call_writes_only_its_outputs(shape, flags):
     """Calls the library with raw pointers.  Every output lives inside a larger poisoned
     buffer; the guard bands before and after it must be untouched."""
@@ -686,24 +691,118 @@ def test_c_abi_direct_call_writes_only_its_outputs(shape, flags):
     part_w, partials = guarded(rows * r, torch.float32)
     dq_w, dq = guarded(r, BF16)
     dq32_w, dq32 = guarded(r, torch.float32)
+    res_w, residual = guarded(n * d, BF16)
+    saved = dict(out_ptr=out.data_ptr(), residual_ptr=residual.data_ptr()) if flags == 2 else {}
     stream = torch.cuda.current_stream().cuda_stream
     step = n * d * 2
     src = [values.data_ptr() + i * step for i in range(s)]
     _native.forward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, 1.0,
-                    out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream)
+                    out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream,
+                    residual_ptr=saved.get("residual_ptr"))
     _native.backward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, 1.0,
                      upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
                      [dv.data_ptr() + i * step for i in range(s)], [d] * s,
-                     partials.data_ptr(), rows, dq.data_ptr(), dq32.data_ptr(), flags, stream)
+                     partials.data_ptr(), rows, dq.data_ptr(), dq32.data_ptr(), flags, stream,
+                     **saved)
     torch.cuda.synchronize()
-    for whole in (out_w, logit_w, stat_w, dv_w, part_w, dq_w, dq32_w):
+    for whole in (out_w, logit_w, stat_w, dv_w, part_w, dq_w, dq32_w, res_w):
         assert bool((whole[:pad] == -7.0).all()) and bool((whole[-pad:] == -7.0).all())
+    if flags != 2:
+        assert bool((residual == -7.0).all()), "the residual was written without being asked for"
     e_out, e_dv, e_dq = ao.oracle_with_grads(values, query, upstream)
     _check_triplet((out.view(n, d), dv.view(s, n, d), dq), (e_out, e_dv, e_dq))
     # FP32 and BF16 forms of the query gradient agree, and the saved statistics are sane.
     assert torch.equal(dq32.to(BF16), dq)
     probs = torch.exp(logits.view(s, n) - stats[:n]) * stats[n:]
     torch.testing.assert_close(probs.sum(0), torch.ones(n, device=dev), rtol=1e-4, atol=1e-4)
+
+
+# ------------------------------------------------------------------ one-pass backward
+
+def _abi_forward_backward(values, query, upstream, *, flags, save, scale=1.0, eps=2**-23):
+    """Forward + backward through the C ABI on contiguous inputs; returns
+    (out, residual or None, dvalues, dquery FP32)."""
+    from attnres import _native
+    s, n, d = values.shape
+    r = query.numel()
+    out = torch.empty(n, d, device="cuda", dtype=BF16)
+    residual = torch.empty(n, d, device="cuda", dtype=BF16) if save else None
+    logits = torch.empty(s, n, device="cuda", dtype=torch.float32)
+    stats = torch.empty(2, n, device="cuda", dtype=torch.float32)
+    dv = torch.empty_like(values)
+    rows = _native.dq_workspace_rows(n, s, d, r, 0)
+    partials = torch.empty(rows, r, device="cuda", dtype=torch.float32)
+    dq = torch.empty(r, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    step = n * d * 2
+    src = [values.data_ptr() + i * step for i in range(s)]
+    _native.forward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, eps, scale,
+                    out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream,
+                    residual_ptr=residual.data_ptr() if save else None)
+    _native.backward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, eps, scale,
+                     upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
+                     [dv.data_ptr() + i * step for i in range(s)], [d] * s,
+                     partials.data_ptr(), rows, None, dq.data_ptr(), flags, stream,
+                     out_ptr=out.data_ptr() if save else None,
+                     residual_ptr=residual.data_ptr() if save else None)
+    torch.cuda.synchronize()
+    return out, residual, dv, dq
+
+
+@pytest.mark.parametrize("shape,flags", [((9, 300, 2048, 2048), 0), ((49, 200, 4096, 1024), 0),
+                                         ((5, 33, 200, 72), 0), ((9, 300, 2048, 2048), 1)],
+                         ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else str(v))
+def test_output_residual_holds_what_the_rounding_dropped(shape, flags):
+    """out + residual reproduces the exact result to about 16 mantissa bits, and asking for
+    the residual does not change `out`."""
+    torch.manual_seed(11)
+    s, n, d, r = shape
+    values = torch.randn(s, n, d, device="cuda", dtype=BF16)
+    query = torch.randn(r, device="cuda", dtype=BF16) * 0.1
+    upstream = torch.randn(n, d, device="cuda", dtype=BF16)
+    out, residual, _, _ = _abi_forward_backward(values, query, upstream, flags=flags, save=True)
+    plain, _, _, _ = _abi_forward_backward(values, query, upstream, flags=flags, save=False)
+    assert torch.equal(out, plain)
+    exact = ao.closed_form(values.double().cpu().numpy(), query.double().cpu().numpy())
+    exact = torch.from_numpy(exact).cuda()
+    # FP32 arithmetic leaves a few 1e-6 of absolute error in the logits' softmax; beyond
+    # that the pair is good to 2^-16 relative, the BF16 output alone only to 2^-9.
+    one = (out.double() - exact).abs()
+    two = (out.double() + residual.double() - exact).abs()
+    assert bool((two <= 2.0**-16 * exact.abs() + 4e-6).all()), two.max().item()
+    assert two.max().item() < one.max().item() / 64, (one.max().item(), two.max().item())
+
+
+STREAM_SHAPES = [
+    (49, 2000, 2048, 2048), (49, 1400, 4096, 4096), (17, 1400, 4096, 4096),
+    (97, 1000, 4096, 64), (129, 500, 8192, 8192), (129, 500, 8192, 1024),
+    (33, 2500, 1536, 128), (49, 2500, 1024, 1024), (5, 3000, 1024, 1024), (7, 700, 256, 256),
+    (6, 2000, 3072, 3064),
+]
+
+
+@pytest.mark.parametrize("shape", STREAM_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_one_pass_backward_matches_the_oracle_and_the_two_pass_kernels(shape):
+    """The streaming backward (several positions per warp group, so the ring wraps and the
+    logits buffers rotate) against the oracle and against the staged kernels."""
+    from attnres import _native
+    torch.manual_seed(20261125)
+    s, n, d, r = shape
+    values = torch.randn(s, n, d, device="cuda", dtype=BF16)
+    query = torch.randn(r, device="cuda", dtype=BF16) * (0.02 if r == d else 0.25)
+    upstream = torch.randn(n, d, device="cuda", dtype=BF16)
+    scale = 1.0 if r == d else r ** -0.5
+    out, _, dv, dq = _abi_forward_backward(values, query, upstream, scale=scale, save=True,
+                                           flags=_native.FLAG_PREFER_STREAM)
+    out2, _, dv2, dq2 = _abi_forward_backward(values, query, upstream, scale=scale, save=False,
+                                              flags=0)
+    assert torch.equal(out, out2)
+    e_out, e_dv, e_dq = ao.oracle_with_grads(values, query, upstream, scale=scale)
+    _check_triplet((out, dv, dq.to(BF16)), (e_out, e_dv, e_dq))
+    # the two kernels round the same FP32 quantities: they differ by single BF16 ulps
+    assert ((dv.float() - dv2.float()).abs() <= 2.0**-6 * dv2.float().abs() + 1e-3).all()
+    torch.testing.assert_close(dq, dq2, rtol=2e-3, atol=2e-3 * dq2.abs().max().item())
+    assert _native.error_flag() == 0
 
 
 def test_no_kernel_gave_up_waiting():
