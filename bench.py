@@ -45,6 +45,7 @@ SOURCE_COUNTS = (2, 5, 9, 17, 25, 49)
 WIDTHS = (1024, 2048, 4096)
 CELLS = [(s, d) for d in WIDTHS for s in SOURCE_COUNTS]
 CPU_SAMPLE_ROWS = 512
+E2E_BLOCK_ROWS = 4096   # rows per host-to-device block of the end-to-end leg
 SEED = 20260827
 METRIC = "attnres_fwd_bwd_tokens_per_s"
 WORKLOAD = "config2_operator_sweep_packed_S{2,5,9,17,25,49}xD{1024,2048,4096}_N16384_R=D"
@@ -410,44 +411,94 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
 
 def run_e2e(args, cells, device, distributed) -> dict:
     """The same sweep through `attnres()` + autograd with every input starting in pinned
-    host memory and every result (out, value gradients, query gradient) copied back."""
+    host memory and every result (out, value gradients, query gradient) copied back.
+
+    Three streams form a pipeline, as a training loop that feeds from host memory would.
+    Positions are independent, so every cell is fed in blocks of E2E_BLOCK_ROWS rows: while
+    block i runs its forward and backward, the inputs of block i+1 cross PCIe host-to-device
+    and the results of block i-1 cross it device-to-host (the link is full duplex).  The
+    query gradient of a cell is the FP32 sum of its blocks' BF16 gradients, rounded once (what
+    gradient accumulation into an FP32 master gives).  Every byte still moves inside the
+    timed region, every step."""
     import torch.distributed as dist
     from attnres import attnres
     steps = max(1, min(args.steps, 3))
     max_elems = max(c.S * ROWS * c.D for c in cells)
+    max_row = ROWS * max(WIDTHS)
+    block_rows = min(E2E_BLOCK_ROWS, ROWS)
+    block_elems = max(c.S * block_rows * c.D for c in cells)
+    block_row = block_rows * max(WIDTHS)
     host_values = torch.empty(max_elems, dtype=torch.bfloat16).pin_memory()
     host_grads = torch.empty(max_elems, dtype=torch.bfloat16).pin_memory()
-    host_up = torch.empty(ROWS * max(WIDTHS), dtype=torch.bfloat16).pin_memory()
-    host_out = torch.empty(ROWS * max(WIDTHS), dtype=torch.bfloat16).pin_memory()
+    host_up = torch.empty(max_row, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(max_row, dtype=torch.bfloat16).pin_memory()
     host_query = torch.empty(max(WIDTHS), dtype=torch.bfloat16).pin_memory()
     host_dq = torch.empty(max(WIDTHS), dtype=torch.bfloat16).pin_memory()
     host_values.normal_()
     host_up.normal_()
     host_query.normal_(std=0.02)
+    # Two sets of device input buffers: one being filled while the other is computed on.
+    dev_values = [torch.empty(block_elems, device=device, dtype=torch.bfloat16) for _ in range(2)]
+    dev_up = [torch.empty(block_row, device=device, dtype=torch.bfloat16) for _ in range(2)]
+    dev_query = [torch.empty(max(WIDTHS), device=device, dtype=torch.bfloat16) for _ in range(2)]
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    compute = torch.cuda.current_stream(device)
+    computed = [None, None]   # event: the cell that last used input set k has finished
     h2d = d2h = 0
 
     def one_step(count):
         nonlocal h2d, d2h
+        turn = 0
         for cell in cells:
-            n_values = cell.S * ROWS * cell.D
-            values = host_values[:n_values].view(cell.S, ROWS, cell.D).to(device, non_blocking=True)
-            query = host_query[:cell.D].to(device, non_blocking=True)
-            upstream = host_up[:ROWS * cell.D].view(ROWS, cell.D).to(device, non_blocking=True)
-            values.requires_grad_()
-            query.requires_grad_()
-            out = attnres(values, query)
-            dv, dq = torch.autograd.grad(out, (values, query), upstream)
+            host_v = host_values[:cell.S * ROWS * cell.D].view(cell.S, ROWS, cell.D)
+            host_g = host_grads[:cell.S * ROWS * cell.D].view(cell.S, ROWS, cell.D)
+            host_u = host_up[:ROWS * cell.D].view(ROWS, cell.D)
+            host_o = host_out[:ROWS * cell.D].view(ROWS, cell.D)
+            dq32 = torch.zeros(cell.D, device=device, dtype=torch.float32)
+            for first in range(0, ROWS, block_rows):
+                rows = min(block_rows, ROWS - first)
+                k, turn = turn % 2, turn + 1
+                values = dev_values[k][:cell.S * rows * cell.D].view(cell.S, rows, cell.D)
+                upstream = dev_up[k][:rows * cell.D].view(rows, cell.D)
+                query = dev_query[k][:cell.D]
+                with torch.cuda.stream(copy_in):
+                    if computed[k] is not None:
+                        copy_in.wait_event(computed[k])
+                    for source in range(cell.S):      # one contiguous copy per source
+                        values[source].copy_(host_v[source, first:first + rows], non_blocking=True)
+                    upstream.copy_(host_u[first:first + rows], non_blocking=True)
+                    query.copy_(host_query[:cell.D], non_blocking=True)
+                    arrived = copy_in.record_event()
+                compute.wait_event(arrived)
+                values.requires_grad_()
+                query.requires_grad_()
+                out = attnres(values, query)
+                dv, dq = torch.autograd.grad(out, (values, query), upstream)
+                dq32 += dq.float()
+                computed[k] = compute.record_event()
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(computed[k])
+                    host_o[first:first + rows].copy_(out, non_blocking=True)
+                    for source in range(cell.S):
+                        host_g[source, first:first + rows].copy_(dv[source], non_blocking=True)
+                for tensor in (out, dv):
+                    tensor.record_stream(copy_out)     # keep the blocks until the copy has run
+                values.requires_grad_(False)
+                query.requires_grad_(False)
+                del out, dv, dq
             if distributed:
-                dq32 = dq.float()
                 dist.all_reduce(dq32)
-                dq = dq32.to(torch.bfloat16)
-            host_out[:ROWS * cell.D].view(ROWS, cell.D).copy_(out, non_blocking=True)
-            host_grads[:n_values].view(cell.S, ROWS, cell.D).copy_(dv, non_blocking=True)
-            host_dq[:cell.D].copy_(dq, non_blocking=True)
+            dq = dq32.to(torch.bfloat16)
+            done = compute.record_event()
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                host_dq[:cell.D].copy_(dq, non_blocking=True)
+            dq.record_stream(copy_out)
             if count:
-                h2d += 2 * (n_values + cell.D + ROWS * cell.D)
-                d2h += 2 * (n_values + cell.D + ROWS * cell.D)
-            del values, query, upstream, out, dv, dq
+                moved = 2 * (cell.S * ROWS * cell.D + ROWS * cell.D)
+                h2d += moved + 2 * cell.D * ((ROWS + block_rows - 1) // block_rows)
+                d2h += moved + 2 * cell.D
+        compute.wait_stream(copy_out)
 
     one_step(False)
     if distributed:

@@ -119,6 +119,9 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
   return launch_bwd_generic<1, 32, 256, 2>(p, grid, st);
 }
 
+// Rows of the dquery workspace per SM: one per resident position stream.  (Twelve rows for
+// D <= 1024, where four one-warp groups per CTA would allow three CTAs per SM instead of two,
+// measured no faster.)
 constexpr int kWorkspaceRowsPerSm = 8;
 
 // The one-pass backward moves 6*D more bytes per position (the forward writes one more BF16
