@@ -576,7 +576,50 @@ def run_single_cell(args) -> None:
     bwd_bytes = rows * (4 * sources * width + 2 * width)
     peak, _ = measured_peak_gbs()
     f, b = sorted(fwd_ms)[len(fwd_ms) // 2], sorted(bwd_ms)[len(bwd_ms) // 2]
-    print(json.dumps({"cell": [sources, rows, width, rank], "fwd_ms": f, "bwd_ms": b,
+    extra = {}
+    if args.accumulate:
+        # Running gradient buffers: (a) this backward followed by the elementwise add autograd
+        # would run, (b) the backward that adds in the kernel (needs the saved output).
+        buffer = torch.zeros_like(values)
+        if residual is None:
+            residual = torch.empty_like(out)
+            _native.forward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
+                            query.data_ptr(), 1, 2**-23, scale, out.data_ptr(), width,
+                            logits.data_ptr(), stats.data_ptr(), flags, stream,
+                            residual_ptr=residual.data_ptr())
+        acc = [buffer.data_ptr() + s * step for s in range(sources)]
+        add_ms, fused_ms = [], []
+        for index in range(args.warmup + args.steps):
+            flush.zero_()
+            a0, a1 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            a0.record()
+            _native.backward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
+                             query.data_ptr(), 1, 2**-23, scale, upstream.data_ptr(), width, 1,
+                             logits.data_ptr(), stats.data_ptr(), dst, [width] * sources,
+                             partials.data_ptr(), partial_rows, dq.data_ptr(), None, flags, stream,
+                             **saved)
+            buffer.add_(grad)
+            a1.record()
+            flush.zero_()
+            b0, b1 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            b0.record()
+            _native.backward(src, [width] * sources, [1] * sources, sources, rows, width, rank,
+                             query.data_ptr(), 1, 2**-23, scale, upstream.data_ptr(), width, 1,
+                             logits.data_ptr(), stats.data_ptr(), acc, [width] * sources,
+                             partials.data_ptr(), partial_rows, dq.data_ptr(), None,
+                             flags | _native.FLAG_ACCUMULATE_DV, stream,
+                             out_ptr=out.data_ptr(), residual_ptr=residual.data_ptr())
+            b1.record()
+            torch.cuda.synchronize()
+            if index >= args.warmup:
+                add_ms.append(a0.elapsed_time(a1))
+                fused_ms.append(b0.elapsed_time(b1))
+        a, fu = sorted(add_ms)[len(add_ms) // 2], sorted(fused_ms)[len(fused_ms) // 2]
+        acc_bytes = rows * (6 * sources * width + 2 * width)   # values, old sums, new sums, dO
+        extra = {"bwd_then_add_ms": a, "bwd_accumulate_ms": fu, "accumulate_speedup": a / fu,
+                 "bwd_accumulate_gbs": acc_bytes / fu / 1e6,
+                 "bwd_accumulate_frac": acc_bytes / fu / 1e6 / peak}
+    print(json.dumps({"cell": [sources, rows, width, rank], "fwd_ms": f, "bwd_ms": b, **extra,
                       "fwd_gbs": fwd_bytes / f / 1e6, "bwd_gbs": bwd_bytes / b / 1e6,
                       "fwd_frac": fwd_bytes / f / 1e6 / peak, "bwd_frac": bwd_bytes / b / 1e6 / peak,
                       "family_fwd": _native.kernel_family(sources, width, rank, True, False)
@@ -601,6 +644,8 @@ def main() -> None:
     parser.add_argument("--generic", action="store_true", help="--cell: force the generic kernels")
     parser.add_argument("--one-pass", action="store_true",
                         help="--cell: save the output residual and prefer the one-pass backward")
+    parser.add_argument("--accumulate", action="store_true",
+                        help="--cell: also time the backward that adds into running gradient buffers")
     parser.add_argument("--two-pass", action="store_true",
                         help="--cell: never save the output residual (staged backward)")
     args = parser.parse_args()

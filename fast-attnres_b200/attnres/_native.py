@@ -12,6 +12,7 @@ from pathlib import Path
 ABI_VERSION = 2
 FLAG_FORCE_GENERIC = 1
 FLAG_PREFER_STREAM = 2
+FLAG_ACCUMULATE_DV = 4
 LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / "libattnres_b200.so"
 
 _PTR_ARRAY = ctypes.POINTER(c_void_p)

@@ -95,14 +95,17 @@ def _packed_table(values):
         [feat_stride] * count
 
 
-def _run_forward(kept, ptrs, row_strides, feat_strides, shape, query, eps, scale):
+def _run_forward(kept, ptrs, row_strides, feat_strides, shape, query, eps, scale,
+                 keep_residual=None):
     S, D, R, N = len(ptrs), int(shape[-1]), int(query.numel()), _rows(shape)
     device = query.device
     out = torch.empty(tuple(shape), device=device, dtype=torch.bfloat16)
     logits = torch.empty((S, N), device=device, dtype=torch.float32)
     stats = torch.empty((2, N), device=device, dtype=torch.float32)
     # A 0-element residual means "not saved": the backward then takes the two-pass kernels.
-    residual = torch.empty(tuple(shape) if _save_residual(S, D, R) else (0,), device=device,
+    if keep_residual is None:
+        keep_residual = _save_residual(S, D, R)
+    residual = torch.empty(tuple(shape) if keep_residual else (0,), device=device,
                            dtype=torch.bfloat16)
     with torch.cuda.device(device):
         _native.forward(ptrs, row_strides, feat_strides, S, N, D, R,
@@ -116,7 +119,7 @@ def _run_forward(kept, ptrs, row_strides, feat_strides, shape, query, eps, scale
 
 def _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output, logits,
                   stats, out, residual, eps, scale, grad_ptrs, need_query,
-                  query_grad_dtype=torch.bfloat16):
+                  query_grad_dtype=torch.bfloat16, extra_flags=0):
     S, D, R, N = len(ptrs), int(shape[-1]), int(query.numel()), _rows(shape)
     device = query.device
     upstream, go_row_stride, go_feat_stride = row_layout(grad_output.reshape(tuple(shape)))
@@ -138,7 +141,7 @@ def _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_outp
             None if partials is None else partials.data_ptr(), partial_rows,
             grad_query.data_ptr() if need_query and not as_f32 else None,
             grad_query.data_ptr() if need_query and as_f32 else None,
-            _flags, _stream(device),
+            _flags | extra_flags, _stream(device),
             out_ptr=out.data_ptr() if saved else None,
             residual_ptr=residual.data_ptr() if saved else None)
     del kept, upstream

@@ -278,10 +278,13 @@ extern "C" int attnres_b200_backward(
     uint32_t flags, void* stream) {
   if (int st = check_shape(S, N, D, R)) return st;
   if (int st = check_scalars(eps, scale)) return st;
-  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM))
+  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM |
+                ATTNRES_B200_FLAG_ACCUMULATE_DV))
     return ATTNRES_B200_ERR_BAD_FLAGS;
   if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !grad_out || !logits || !stats)
     return ATTNRES_B200_ERR_NULL_POINTER;
+  const bool accumulate = (flags & ATTNRES_B200_FLAG_ACCUMULATE_DV) != 0;
+  if (accumulate && dsrc_ptrs == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
   const bool want_dq = dq_bf16 != nullptr || dq_f32 != nullptr;
   const bool want_dv = dsrc_ptrs != nullptr;
   if (!want_dq && !want_dv) return ATTNRES_B200_ERR_NOTHING_TO_DO;
@@ -310,6 +313,7 @@ extern "C" int attnres_b200_backward(
   p.D = D;
   p.R = R;
   p.write_dv = want_dv ? 1 : 0;
+  p.accumulate = accumulate ? 1 : 0;
   p.N = N;
   p.query = static_cast<const __nv_bfloat16*>(query);
   p.query_stride = query_stride;
@@ -342,11 +346,12 @@ extern "C" int attnres_b200_backward(
     const bool have_saved = out_saved != nullptr && out_residual != nullptr &&
                             aligned16(out_saved) && aligned16(out_residual);
     if (have_saved && bwd_stream_supported(S, D, R) &&
-        ((flags & ATTNRES_B200_FLAG_PREFER_STREAM) || wants_output_residual(S, D, R)))
+        (accumulate || (flags & ATTNRES_B200_FLAG_PREFER_STREAM) || wants_output_residual(S, D, R)))
       st = launch_bwd_stream(p, sms, max_rows, &grid, cs);
-    if (st != ATTNRES_B200_OK && bwd_ring_supported(S, D, R))
+    // Only the one-pass and the generic kernels accumulate.
+    if (st != ATTNRES_B200_OK && !accumulate && bwd_ring_supported(S, D, R))
       st = launch_bwd_ring(p, sms, max_rows, &grid, cs);
-    if (st != ATTNRES_B200_OK && tma_bwd_supported(S, D, R))
+    if (st != ATTNRES_B200_OK && !accumulate && tma_bwd_supported(S, D, R))
       st = launch_bwd_tma(p, sms, max_rows, &grid, cs);
   }
   if (st != ATTNRES_B200_OK) {

@@ -66,7 +66,7 @@ inline bool make_bwd_stream_plan(int S, int D, int R, BwdStreamPlan* plan) {
   const uint32_t bars = (uint32_t)groups * 8u * 8u;
   const uint32_t part = (uint32_t)groups * 2u * kRingMaxGroupWarps * 16u;
   const uint32_t zl = (uint32_t)groups * 3u * kStreamLogitSlots * 4u;
-  const uint32_t tab = (uint32_t)S * (uint32_t)sizeof(StreamRowRef);
+  const uint32_t tab = 2u * (uint32_t)S * (uint32_t)sizeof(StreamRowRef);  // sources, gradients
   const uint32_t fixed = bars + part + zl + tab + 16u + 128u;
   const uint32_t room = (228u * 1024u - (uint32_t)p.ctas_per_sm * 1024u) / (uint32_t)p.ctas_per_sm;
   const uint32_t usable = room < (uint32_t)kSmemPerCtaMax ? room : (uint32_t)kSmemPerCtaMax;
@@ -108,7 +108,10 @@ __device__ __forceinline__ void unpack_pairs(const uint4& raw, float2* f) {
 // of every lane are tail chunks; TAIL0 < 0: per-lane predicates decide.
 // SR (needs FULL): row size and ring depth (eight stages) are compile-time constants.
 // ZE: registers of an absent second source are zero-filled (only changes code placement).
-template <int G, bool FULL, int TAIL0, bool SR, bool ZE>
+// ACC: accumulate.  The existing gradient row of every source travels through the ring right
+// behind the source row (2 S + 3 items per position) and is added in FP32 before the one
+// rounding to BF16; the four stages of a batch are refilled after the gradients are stored.
+template <int G, bool FULL, int TAIL0, bool SR, bool ZE, bool ACC>
 __global__ void __launch_bounds__((G > 4 ? 8 : 4) * 32, G > 4 ? 1 : 3)
 bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdStreamPlan plan) {
   static_assert(TAIL0 < 0 || FULL, "a compile-time tail boundary needs a full row");
@@ -126,7 +129,8 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   const int D = SR ? L * NV * 8 : p.D;
   const int CH = D / 8, c0 = (D - R) / 8;
   const int nst = SR ? kRingStaticStages : plan.stages;
-  const int items = S + 3;  // dO, out, residual, then the sources
+  constexpr int K = ACC ? 2 : 1;  // ring items per source
+  const int items = K * S + 3;    // dO, out, residual, then the sources
   const uint32_t row_bytes = (uint32_t)D * 2u;
   unsigned char* ring = smem + (size_t)group * (size_t)nst * row_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + plan.off_bars) + group * 8;
@@ -135,10 +139,15 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   float* zl_sm = reinterpret_cast<float*>(smem + plan.off_zl) + group * (3 * kStreamLogitSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + plan.off_abort);
   StreamRowRef* src_tab = reinterpret_cast<StreamRowRef*>(smem + plan.off_tab);
+  StreamRowRef* grad_tab = src_tab + S;  // filled and read by the accumulating instances only
 
   for (int s = tid; s < S; s += WARPS * 32) {
     src_tab[s].base = reinterpret_cast<uint64_t>(p.src.ptr[s]);
     src_tab[s].row_stride = p.src.row_stride[s];
+    if (ACC) {
+      grad_tab[s].base = reinterpret_cast<uint64_t>(p.grad.ptr[s]);
+      grad_tab[s].row_stride = p.grad.row_stride[s];
+    }
   }
   if (tid == 0) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + plan.off_bars);
@@ -190,7 +199,8 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
     else if (issue_item == 1) src = p.out_saved + issue_row * (int64_t)D;
     else if (issue_item == 2) src = p.out_residual + issue_row * (int64_t)D;
     else {
-      const StreamRowRef ref = src_tab[issue_item - 3];
+      const int k = issue_item - 3;
+      const StreamRowRef ref = ACC ? ((k & 1) ? grad_tab[k >> 1] : src_tab[k >> 1]) : src_tab[k];
       src = reinterpret_cast<const __nv_bfloat16*>(ref.base) + issue_row * ref.row_stride;
     }
     mbar_expect_tx(&full_bar[issue_stage], row_bytes);
@@ -301,7 +311,7 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
         if (b < NB) {
           uint4(&mine)[NV] = raw[b];
           uint32_t phase;
-          const int stage = cursor.stage(b, &phase);
+          const int stage = cursor.stage(b * K, &phase);
           mbar_wait_fast(&full_bar[stage], phase, abort_flag);
           const uint4* vrow = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
 #pragma unroll
@@ -355,12 +365,14 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
           tot[3] += t.w;
         }
       }
-      if (leader) {
-        fence_proxy_async();
-        in_flight -= NB;
-        while (rows_to_issue > 0 && in_flight < nst) issue_one();
+      if (!ACC) {
+        if (leader) {
+          fence_proxy_async();
+          in_flight -= NB;
+          while (rows_to_issue > 0 && in_flight < nst) issue_one();
+        }
+        cursor.advance(NB);
       }
-      cursor.advance(NB);
 
       // ---- finish the batch from the chunks still in registers
 #pragma unroll
@@ -375,6 +387,13 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
         const float2 ps2 = make_float2(prob, prob), ca2 = make_float2(ca, ca),
                      ncb2 = make_float2(-cb, -cb);
         __nv_bfloat16* out_row = p.write_dv ? p.grad.ptr[s] + row * p.grad.row_stride[s] : nullptr;
+        const uint4* old_row = nullptr;
+        if (ACC) {
+          uint32_t phase;
+          const int stage = cursor.stage(b * K + 1, &phase);
+          mbar_wait_fast(&full_bar[stage], phase, abort_flag);
+          old_row = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
+        }
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
           if (row_ok(j)) {
@@ -391,6 +410,12 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
               }
             }
             if (out_row != nullptr) {
+              if (ACC) {
+                float2 old[4];
+                unpack_pairs(old_row[j * L], old);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) dv[k] = __fadd2_rn(dv[k], old[k]);
+              }
               uint4 packed;
               packed.x = pack_bf16x2(dv[0].x, dv[0].y);
               packed.y = pack_bf16x2(dv[1].x, dv[1].y);
@@ -400,6 +425,18 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
             }
           }
         }
+      }
+      if (ACC) {
+        // The old gradient rows were read from the ring during the stores: every lane of the
+        // group must be past them before the leader refills the batch's stages.
+        if (G > 1) group_sync(group, L);
+        else __syncwarp();
+        if (leader) {
+          fence_proxy_async();
+          in_flight -= K * NB;
+          while (rows_to_issue > 0 && in_flight < nst) issue_one();
+        }
+        cursor.advance(K * NB);
       }
       buf ^= 1;
     };
@@ -424,10 +461,10 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
   }
 }
 
-template <int G, bool FULL, int TAIL0, bool SR, bool ZE>
+template <int G, bool FULL, int TAIL0, bool SR, bool ZE, bool ACC>
 inline int launch_bwd_stream_variant(const BwdParams& p, const BwdStreamPlan& plan, int grid,
                                      cudaStream_t stream) {
-  auto kernel = bwd_stream_kernel<G, FULL, TAIL0, SR, ZE>;
+  auto kernel = bwd_stream_kernel<G, FULL, TAIL0, SR, ZE, ACC>;
   if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
   kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
@@ -437,16 +474,28 @@ inline int launch_bwd_stream_variant(const BwdParams& p, const BwdStreamPlan& pl
 // algorithmic bytes at S = 49, best against worst combination):
 //   G = 1 (D = 1024): all three on, 5141 against 3484;   G = 2 (D = 2048): SR + ZE, 6186 / 5375;
 //   G = 4 (D = 4096): none, 6336 / 5393 (SR alone costs 14 %);   G = 8 (D = 8192): SR + tail, 6342 / 5489.
-template <int G>
+// The accumulating instances use the same choice.
+template <int G, bool ACC>
 inline int launch_bwd_stream_instance(const BwdParams& p, const BwdStreamPlan& plan, int grid,
                                       cudaStream_t stream) {
   const bool full = p.D / 8 == G * 32 * kRingChunks && plan.stages == kRingStaticStages;
-  if (!full) return launch_bwd_stream_variant<G, false, -1, false, false>(p, plan, grid, stream);
+  if (!full) return launch_bwd_stream_variant<G, false, -1, false, false, ACC>(p, plan, grid, stream);
   constexpr bool SR = G != 4, ZE = G <= 2;
   constexpr int TAIL0 = (G == 1 || G == 8) ? 0 : -1;
   if (TAIL0 == 0 && p.R == p.D)
-    return launch_bwd_stream_variant<G, true, TAIL0, SR, ZE>(p, plan, grid, stream);
-  return launch_bwd_stream_variant<G, true, -1, SR, ZE>(p, plan, grid, stream);
+    return launch_bwd_stream_variant<G, true, TAIL0, SR, ZE, ACC>(p, plan, grid, stream);
+  return launch_bwd_stream_variant<G, true, -1, SR, ZE, ACC>(p, plan, grid, stream);
+}
+
+template <bool ACC>
+inline int launch_bwd_stream_group(const BwdParams& p, const BwdStreamPlan& plan, int grid,
+                                   cudaStream_t stream) {
+  switch (plan.group_warps) {
+    case 1: return launch_bwd_stream_instance<1, ACC>(p, plan, grid, stream);
+    case 2: return launch_bwd_stream_instance<2, ACC>(p, plan, grid, stream);
+    case 4: return launch_bwd_stream_instance<4, ACC>(p, plan, grid, stream);
+    default: return launch_bwd_stream_instance<8, ACC>(p, plan, grid, stream);
+  }
 }
 
 // `max_rows` bounds the dquery partial rows (one per group); the count used is returned.
@@ -462,13 +511,8 @@ inline int launch_bwd_stream(const BwdParams& p, int sms, int max_rows, int* row
   // Fewer positions than one CTA has groups: the idle groups write no partial row.
   if (grid < 1 && p.N <= max_rows) grid = 1;
   if (grid < 1) return 9;
-  int st;
-  switch (plan.group_warps) {
-    case 1: st = launch_bwd_stream_instance<1>(p, plan, (int)grid, stream); break;
-    case 2: st = launch_bwd_stream_instance<2>(p, plan, (int)grid, stream); break;
-    case 4: st = launch_bwd_stream_instance<4>(p, plan, (int)grid, stream); break;
-    default: st = launch_bwd_stream_instance<8>(p, plan, (int)grid, stream); break;
-  }
+  const int st = p.accumulate ? launch_bwd_stream_group<true>(p, plan, (int)grid, stream)
+                              : launch_bwd_stream_group<false>(p, plan, (int)grid, stream);
   const int64_t written = grid * groups < p.N ? grid * groups : p.N;
   *rows_out = (int)written;
   return st;

@@ -56,6 +56,7 @@ struct BwdParams {
   int32_t D;
   int32_t R;
   int32_t write_dv;  // 0: skip the value-gradient stores
+  int32_t accumulate;  // 1: add to the existing value-gradient rows instead of overwriting
   int64_t N;
   const __nv_bfloat16* query;
   int64_t query_stride;

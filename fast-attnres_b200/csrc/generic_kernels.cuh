@@ -300,9 +300,21 @@ bwd_generic_kernel(const __grid_constant__ BwdParams p) {
         for (int j = 0; j < NJ; ++j) {
           const int c = j * T + tid;
           if constexpr (VEC == 8) {
-            if (c * 8 < D) *reinterpret_cast<uint4*>(grow + (int64_t)c * 8) = pack8(dv + j * 8);
+            if (c * 8 < D) {
+              uint4* dst = reinterpret_cast<uint4*>(grow + (int64_t)c * 8);
+              if (p.accumulate) {
+                float old[8];
+                unpack8(*dst, old);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dv[j * 8 + e] += old[e];
+              }
+              *dst = pack8(dv + j * 8);
+            }
           } else {
-            if (c < D) grow[c] = __float2bfloat16_rn(dv[j]);
+            if (c < D) {
+              const float old = p.accumulate ? __bfloat162float(grow[c]) : 0.f;
+              grow[c] = __float2bfloat16_rn(dv[j] + old);
+            }
           }
         }
       }

@@ -68,6 +68,16 @@ extern "C" {
 /* Backward: take the one-pass streaming kernel whenever the saved output is given and the
  * shape allows it, whatever the library's own choice would be (tests, tuning). */
 #define ATTNRES_B200_FLAG_PREFER_STREAM 2u
+/* Backward: ACCUMULATE the value gradients.  Every `dsrc_ptrs[s]` row is read, the gradient of
+ * this call is added to it in FP32 and the sum is rounded to BF16 once: dsrc[s] += dV_s.  For
+ * training loops that own one running gradient buffer per source and read the same sources
+ * many times (the role of autograd's accumulation of the per-read gradients after
+ * src/attnres/_kernels/fixed_tail_sources.py:141-183; the reference has no fused form).
+ * Needs `dsrc_ptrs`.  Runs in the one-pass kernel when the saved output is given and the
+ * layout is in the fast class (pass the forward's `out` and `out_residual`; the forward
+ * writes the residual for any shape when asked), otherwise in the layout-generic kernel.
+ * The query gradient is not accumulated: `dq_*` are overwritten as usual. */
+#define ATTNRES_B200_FLAG_ACCUMULATE_DV 4u
 
 /* Replaces nothing in the reference; lets a binding check it loaded the
  * library it was written against. */

@@ -165,3 +165,32 @@ def test_row_layout_flattens_affine_batches_and_copies_the_rest():
     # a single vector
     tensor, row, feat = row_layout(base[:8])
     assert (row, feat) == (0, 1)
+
+
+def test_accumulate_argument_checks():
+    """`attnres_accumulate` validates like `attnres` and then checks the buffers (CPU only:
+    nothing is launched)."""
+    from attnres.accumulate import attnres_accumulate
+    values = torch.zeros(3, 4, 16, dtype=torch.bfloat16)
+    query = torch.zeros(8, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attnres_accumulate(values, query, torch.zeros_like(values))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attnres_accumulate(list(values.unbind(0)), query, [torch.zeros(4, 16, dtype=torch.bfloat16)] * 3)
+    with pytest.raises(ValueError):
+        attnres_accumulate(values, query, torch.zeros_like(values), eps=0.0)
+    from attnres.accumulate import _check_buffers
+    good = [torch.zeros(4, 16, dtype=torch.bfloat16) for _ in range(3)]
+    shapes = [(4, 16)] * 3
+    _check_buffers(good, shapes, good[0].device)
+    with pytest.raises(ValueError, match="one gradient buffer per source"):
+        _check_buffers(good[:2], shapes, good[0].device)
+    with pytest.raises(TypeError, match="BF16"):
+        _check_buffers([g.float() for g in good], shapes, good[0].device)
+    with pytest.raises(ValueError, match="shape"):
+        _check_buffers([g[:2] for g in good], shapes, good[0].device)
+    with pytest.raises(ValueError, match="contiguous"):
+        _check_buffers([torch.zeros(16, 4, dtype=torch.bfloat16).T for _ in range(3)], shapes,
+                       good[0].device)
+    with pytest.raises(ValueError, match="own gradient buffer"):
+        _check_buffers([good[0], good[0], good[1]], shapes, good[0].device)
