@@ -125,26 +125,34 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
 constexpr int kWorkspaceRowsPerSm = 8;
 
 // The one-pass backward moves 6*D more bytes per position (the forward writes one more BF16
-// row, the backward reads two more) and finishes each source as it arrives.  Measured on
-// B200 against the two-pass kernels (N = 16384, R = D unless noted):
-//   * it wins wherever the staged backward can hold only one position per SM, needs a
-//     cluster or does not fit (S >= 33 at D = 2048/4096, S >= 65 at D = 1024, every S at D = 8192): 1.4x to 5x;
-//   * full-width rows of 2048 and more with R = D: it wins or ties from S = 5 up
-//     (D = 4096: 5.3 vs 3.9 TB/s at S = 5, 6.3 vs 6.0 at S = 25);
+// row, which costs it 1/(S+1) of its time; the backward reads two more) and finishes each
+// source as it arrives.  Measured on B200 against the two-pass kernels, forward and backward
+// together (N = 16384, R = D unless noted):
+//   * it wins wherever the staged backward needs a cluster or does not fit (S >= 33 at
+//     D = 4096, every long list at D = 8192), and for D <= 2048 wherever a position's staged
+//     rows take more than half an SM's shared memory (S >= 33 at D = 2048, S >= 65 at
+//     D = 1024): 1.4x to 5x on the backward;
+//   * full-width rows with R = D: at D >= 4096 it wins from S = 5 up (backward 5.3 vs 3.9 TB/s
+//     at S = 5, 6.3 vs 6.0 at S = 25); at D = 2048 it wins for S = 5..9 (4.7 vs 3.9, 5.2 vs
+//     4.8) and loses the forward's extra row again at S = 17 and 25 (backward within 1 %);
+//   * up to four sources: the register-resident kernel wins (S = 2, 3: 5.7 vs 4.3 TB/s) or
+//     ties once the forward's extra row is counted (S = 4, D = 4096: 388 vs 386 us);
 //   * D <= 1024: it wins only once the staged backward is down to two CTAs per SM (S = 49);
-//   * low-rank tails with a staged backward at two or more CTAs per SM: the two-pass kernels
-//     stay ahead by 3 to 6 %.
+//   * low-rank tails at D = 4096 with a staged backward that fits one SM (S = 16, R = 1024:
+//     5.45 vs 5.31 TB/s) and short low-rank lists: the two-pass kernels stay ahead by 3 to 6 %.
 bool wants_output_residual(int S, int D, int R) {
   BwdStreamPlan stream;
   if (S <= 4 || !make_bwd_stream_plan(S, D, R, &stream)) return false;
   BwdPlan stash;
   if (!make_bwd_plan(S, D, R, &stash)) return true;
+  if (stash.cluster > 1) return true;
   // One position's staged rows take more than half an SM's shared memory: the staged kernel
-  // cannot overlap two positions on an SM, whatever its CTA shape.
+  // cannot overlap two positions on an SM.  (At D = 4096 it runs one wide CTA per SM by
+  // design and holds up until it needs a cluster.)
   const bool one_position_per_sm = (size_t)(S + 1) * (size_t)D * 2u > 114u * 1024u;
-  if (stash.cluster > 1 || one_position_per_sm) return true;
+  if (D <= 2048 && one_position_per_sm) return true;
   const bool full_row = D / 8 == stream.group_warps * 32 * kRingChunks;
-  if (full_row && R == D && D >= 2048) return true;
+  if (full_row && R == D && (D >= 4096 || (D >= 2048 && S <= 12))) return true;
   return D <= 1024 && stash.ctas_per_sm <= 2;
 }
 

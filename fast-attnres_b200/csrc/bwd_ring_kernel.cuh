@@ -15,6 +15,12 @@
 //      registers and accumulate their dquery lanes across all positions of the group.
 // A position therefore costs one barrier, no second read of shared memory and no serial
 // section, and the ring keeps `stages` rows in flight whatever the position's size.
+//
+// Template parameters: G warps per group; SE the exact source count (2..4), or 0 for "any
+// count up to four, tested at run time"; FULL: the row is exactly G*32*2 chunks wide (no lane
+// holds a chunk beyond the row); TAIL0 >= 0 (needs FULL): chunks j >= TAIL0 of every lane are
+// tail chunks, TAIL0 < 0: per-lane predicates.  The exact-count, full-row instances run
+// without any per-source or per-chunk test in the position loop.
 #pragma once
 
 #include "fwd_ring_kernel.cuh"
@@ -93,20 +99,23 @@ inline bool bwd_ring_supported(int S, int D, int R) {
   return make_bwd_ring_plan(S, D, R, &plan);
 }
 
-template <int G, int SMAX>
-__global__ void __launch_bounds__((G > 4 ? G : 4) * 32,
-                                  SMAX == 4 ? (G > 8 ? 1 : G > 4 ? 2 : 4) : (G > 4 ? 1 : 3))
+template <int G, int SE, bool FULL, int TAIL0>
+__global__ void __launch_bounds__((G > 4 ? G : 4) * 32, G > 8 ? 1 : G > 4 ? 2 : 4)
 bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdRingPlan plan) {
+  static_assert(TAIL0 < 0 || FULL, "a compile-time tail boundary needs a full row");
   constexpr int NV = kBwdRingChunks;
   constexpr int WARPS = G > 4 ? G : 4;
   constexpr int GROUPS = WARPS / G;
   constexpr int L = G * 32;
-  constexpr int K = 2 * SMAX;  // values reduced per position: (ss, dw) of every source
+  constexpr int SMAX = SE > 0 ? SE : 4;
+  // Values reduced per position: (ss, dw) of every source, padded to a power of two for the
+  // folded butterfly.
+  constexpr int K = SMAX == 1 ? 2 : SMAX == 2 ? 4 : 8;
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = warp / G, wig = warp % G;
   const int gl = wig * 32 + lane;
-  const int S = p.S, D = p.D, R = p.R;
+  const int S = SE > 0 ? SE : p.S, D = p.D, R = p.R;
   const int CH = D / 8, c0 = (D - R) / 8, nst = plan.stages;
   const int items = S + 1;  // upstream row, then the sources
   const uint32_t row_bytes = (uint32_t)D * 2u;
@@ -126,17 +135,24 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
   }
   __syncthreads();
 
-  bool in_row[NV], in_tail[NV];
+  bool in_row_rt[NV], in_tail_rt[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = gl + j * L;
+    in_row_rt[j] = c < CH;
+    in_tail_rt[j] = in_row_rt[j] && c >= c0;
+  }
+  // With compile-time j these fold to constants in the specialised instances.
+  auto row_ok = [&](int j) { return FULL ? true : in_row_rt[j]; };
+  auto tail_ok = [&](int j) { return TAIL0 >= 0 ? j >= TAIL0 : in_tail_rt[j]; };
   float2 q2[NV][4], dq2[NV][4];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int c = gl + j * L;
-    in_row[j] = c < CH;
-    in_tail[j] = in_row[j] && c >= c0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float lo = 0.f, hi = 0.f;
-      if (in_tail[j]) {
+      if (tail_ok(j)) {
         const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
         lo = __bfloat162float(p.query[r * p.query_stride]);
         hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
@@ -216,7 +232,7 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
         const uint4* src = reinterpret_cast<const uint4*>(ring + (uint32_t)stage * row_bytes) + gl;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-          const uint4 raw = in_row[j] ? src[j * L] : make_uint4(0u, 0u, 0u, 0u);
+          const uint4 raw = row_ok(j) ? src[j * L] : make_uint4(0u, 0u, 0u, 0u);
           if (i == 0) g_raw[j] = raw;
           else v_raw[i - 1][j] = raw;
         }
@@ -249,7 +265,7 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
           v[3] = make_float2(bf16x2_lo(v_raw[s][j].w), bf16x2_hi(v_raw[s][j].w));
 #pragma unroll
           for (int k = 0; k < 4; ++k) dw2 = __ffma2_rn(v[k], g2[j][k], dw2);
-          if (in_tail[j]) {
+          if (tail_ok(j)) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) ss2 = __ffma2_rn(v[k], v[k], ss2);
           }
@@ -258,6 +274,8 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
       val[2 * s] = ss2.x + ss2.y;
       val[2 * s + 1] = dw2.x + dw2.y;
     }
+#pragma unroll
+    for (int i = 2 * SMAX; i < K; ++i) val[i] = 0.f;
     // Folded butterfly: each step halves the number of values a lane carries; afterwards
     // lane (i << shift) holds the warp total of value i, for every i < K.
     {
@@ -274,8 +292,8 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
       }
       for (; offset >= 1; offset /= 2) val[0] += __shfl_xor_sync(0xffffffffu, val[0], offset);
     }
-    constexpr int SHIFT = K == 8 ? 2 : 1;  // 32 / K lanes share one value
-    float tot[K];
+    constexpr int SHIFT = K == 8 ? 2 : K == 4 ? 3 : 4;  // 32 / K lanes share one value
+    float tot[K < 4 ? 4 : K];
     if (G == 1) {
 #pragma unroll
       for (int i = 0; i < K; ++i) tot[i] = __shfl_sync(0xffffffffu, val[0], i << SHIFT);
@@ -284,11 +302,11 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
       if ((lane & ((1 << SHIFT) - 1)) == 0) mine[wig * (2 * kBwdRingMaxSources) + (lane >> SHIFT)] = val[0];
       group_sync(group, L);
 #pragma unroll
-      for (int i = 0; i < K; ++i) tot[i] = 0.f;
+      for (int i = 0; i < (K < 4 ? 4 : K); ++i) tot[i] = 0.f;
 #pragma unroll
       for (int w = 0; w < G; ++w) {
 #pragma unroll
-        for (int i = 0; i < K; i += 4) {
+        for (int i = 0; i < K; i += 4) {  // whole float4s; slots beyond K hold stale values
           const float4 t = *reinterpret_cast<const float4*>(&mine[w * (2 * kBwdRingMaxSources) + i]);
           tot[i] += t.x;
           tot[i + 1] += t.y;
@@ -332,11 +350,11 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
         __nv_bfloat16* out_row = p.write_dv ? p.grad.ptr[s] + row * p.grad.row_stride[s] : nullptr;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-          if (in_row[j]) {
+          if (row_ok(j)) {
             float2 dv[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) dv[k] = __fmul2_rn(ps2, g2[j][k]);
-            if (in_tail[j]) {
+            if (tail_ok(j)) {
               float2 v[4];
               v[0] = make_float2(bf16x2_lo(v_raw[s][j].x), bf16x2_hi(v_raw[s][j].x));
               v[1] = make_float2(bf16x2_lo(v_raw[s][j].y), bf16x2_hi(v_raw[s][j].y));
@@ -367,7 +385,7 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
     float* prow = p.dq_partials + gid * R;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-      if (in_tail[j]) {
+      if (tail_ok(j)) {
         float4* dst = reinterpret_cast<float4*>(prow + (int64_t)(gl + j * L - c0) * 8);
         dst[0] = make_float4(dq2[j][0].x, dq2[j][0].y, dq2[j][1].x, dq2[j][1].y);
         dst[1] = make_float4(dq2[j][2].x, dq2[j][2].y, dq2[j][3].x, dq2[j][3].y);
@@ -381,20 +399,37 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
   }
 }
 
-template <int G, int SMAX>
+template <int G, int SE, bool FULL, int TAIL0>
 inline int launch_bwd_ring_instance(const BwdParams& p, const BwdRingPlan& plan, int grid,
                                     cudaStream_t stream) {
-  if (int st = prepare_kernel(bwd_ring_kernel<G, SMAX>, plan.smem_bytes)) return st;
-  bwd_ring_kernel<G, SMAX><<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
+  auto kernel = bwd_ring_kernel<G, SE, FULL, TAIL0>;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }
 
+template <int G, int SE>
+inline int launch_bwd_ring_tail(const BwdParams& p, const BwdRingPlan& plan, int grid,
+                                cudaStream_t stream) {
+  if (p.R == p.D) return launch_bwd_ring_instance<G, SE, true, 0>(p, plan, grid, stream);
+  return launch_bwd_ring_instance<G, SE, true, -1>(p, plan, grid, stream);
+}
+
+// Only lists of up to four sources run here: with five to eight sources in registers the
+// kernel measured slower than the staged backward (3.3 vs 3.9 TB/s at S=5, D=4096).  Full
+// rows with two or three sources get the exact-count instances (with four the compiler
+// interleaves all sources and spills 150 to 380 bytes per thread); everything else the
+// run-time form.
 template <int G>
 inline int launch_bwd_ring_smax(const BwdParams& p, const BwdRingPlan& plan, int grid,
                                 cudaStream_t stream) {
-  // Only the four-source instance is built: with five to eight sources in registers the
-  // kernel measured slower than the staged backward (3.3 vs 3.9 TB/s at S=5, D=4096).
-  return launch_bwd_ring_instance<G, 4>(p, plan, grid, stream);
+  if constexpr (G <= 8) {
+    if (p.D / 8 == G * 32 * kBwdRingChunks) {
+      if (p.S == 2) return launch_bwd_ring_tail<G, 2>(p, plan, grid, stream);
+      if (p.S == 3) return launch_bwd_ring_tail<G, 3>(p, plan, grid, stream);
+    }
+  }
+  return launch_bwd_ring_instance<G, 0, false, -1>(p, plan, grid, stream);
 }
 
 // `max_rows` bounds the dquery partial rows (one per group); the count used is returned.

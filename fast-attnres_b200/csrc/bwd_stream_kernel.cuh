@@ -1,5 +1,5 @@
-// One-pass streaming backward of the AttnRes read for LONG source lists in the aligned
-// layout (feature stride 1, 16-byte aligned rows, D and D-R multiples of 8).
+// One-pass streaming backward of the AttnRes read for the aligned layout (feature stride 1,
+// 16-byte aligned rows, D and D-R multiples of 8).
 //
 // The staged ("stash") backward needs all S rows of a position in shared memory because
 // delta = sum_s p_s (v_s . dO) is only known after every source has been reduced.  When the
@@ -17,8 +17,11 @@
 //
 // Shared memory holds only the ring, so any S fits, three CTAs stay resident per SM and the
 // loads of later sources overlap the stores of earlier ones.  The price is 6*D extra bytes per
-// position (one more BF16 row written by the forward, two more read here), which is why the
-// library chooses this kernel only where the staged backward is limited to one CTA per SM.
+// position (one more BF16 row written by the forward, two more read here); which shapes take
+// this kernel is decided by attnres_b200_wants_output_residual from measurements.
+//
+// In accumulate mode (template parameter ACC) the existing gradient row of every source rides
+// the ring behind the source row and is added before the store: dsrc[s] += dV_s.
 #pragma once
 
 #include "fwd_ring_kernel.cuh"

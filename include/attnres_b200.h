@@ -148,7 +148,10 @@ int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t 
  *   out_residual       contiguous).  Both or neither; NULL for both is always correct.
  *   dsrc_ptrs[s]       device BF16 [N,D] gradient of source s, row stride
  *                      dsrc_row_stride[s], feature stride 1 (host arrays, length S).
- *                      NULL skips the value gradients.
+ *                      NULL skips the value gradients.  Overwritten, or with
+ *                      ATTNRES_B200_FLAG_ACCUMULATE_DV added to (the S buffers must
+ *                      then be distinct and must not overlap: a row is fetched before
+ *                      it is updated).
  *   dq_partials        device FP32 workspace [dq_partial_rows, R]
  *   dq_bf16, dq_f32    device [R] outputs, contiguous; either may be NULL.  The
  *                      FP32 form is the one to all-reduce across GPUs before the

@@ -91,7 +91,11 @@ def test_output_residual_policy_is_a_pure_host_decision():
     assert not _native.wants_output_residual(2, 1024, 1024)
     assert not _native.wants_output_residual(4, 4096, 4096)
     assert not _native.wants_output_residual(25, 1024, 1024)
+    assert not _native.wants_output_residual(25, 2048, 2048)
     assert not _native.wants_output_residual(7, 4096, 1024)
+    assert not _native.wants_output_residual(16, 4096, 1024)
+    assert _native.wants_output_residual(25, 4096, 4096)
+    assert _native.wants_output_residual(33, 2048, 512)
     assert _native.wants_output_residual(9, 2048, 2048)
     assert _native.wants_output_residual(49, 1024, 1024)
     assert _native.wants_output_residual(49, 2048, 2048)
