@@ -16,7 +16,13 @@ replayed; CUDA events around each replay, median reported.  The model itself run
 
 Arms: ``ours-list`` (sources passed as a tuple, no packing copy), ``ours-packed``
 (``torch.stack`` then the packed operator, the reference model's default layout),
-``triton-packed`` (reference package from ``baseline/_ref``).  The reference's list-layout
+``triton-packed`` (reference package from ``baseline/_ref``), and ``ours-accumulate``: the list
+layout with a staged backward that owns one running gradient buffer per sublayer output.  Every
+read takes DETACHED sources and adds its value gradients to those buffers inside the backward
+kernel (``attnres.accumulate.attnres_accumulate``); after the loss's backward has run the last
+read, the sublayer outputs are back-propagated one by one, newest first, each with its finished
+buffer as the incoming gradient.  Autograd then never materialises or sums the 1 224 per-read
+source gradients.  The reference's list-layout
 Triton path autotunes 48 configurations for each of 96 kernel specialisations of this model
 and is not run here for GPU-time reasons.
 """
@@ -29,7 +35,7 @@ import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
-ARMS = ("triton-packed", "ours-packed", "ours-list")
+ARMS = ("triton-packed", "ours-packed", "ours-list", "ours-accumulate")
 
 
 def build_model(torch, operator, layout, layers, width, heads, ffn, vocab, sequence):
@@ -83,6 +89,34 @@ def build_model(torch, operator, layout, layers, width, heads, ffn, vocab, seque
                 return operator(torch.stack(sources), query)
             return operator(tuple(sources), query)
 
+        def forward_staged(self, tokens, accumulate, buffers):
+            """Forward for the staged backward: returns (logits, sublayer outputs still attached
+            to their own graph segment, the detached embedding the first attention consumed)."""
+            bf16 = lambda t: t.to(torch.bfloat16)
+            embedded = bf16(self.token_embedding(tokens) + self.position_embedding[: tokens.shape[-1]])
+            attached, sources = [embedded], [embedded.detach()]
+            first_input = embedded.detach().requires_grad_()
+            last = 2 * len(self.layers)
+
+            def read(index):
+                query = self.queries[index].to(torch.bfloat16)
+                # the LAST read runs its backward first and touches every buffer: it overwrites
+                return accumulate(tuple(sources), query, buffers[: len(sources)],
+                                  overwrite=index == last)
+
+            x, reads = first_input, 0
+            for index, layer in enumerate(self.layers):
+                if index > 0:
+                    x = read(reads)
+                    reads += 1
+                attached.append(bf16(layer.attention(x)))
+                sources.append(attached[-1].detach())
+                x = read(reads)
+                reads += 1
+                attached.append(bf16(layer.mlp(x)))
+                sources.append(attached[-1].detach())
+            return self.lm_head(read(reads)), attached, first_input
+
         def forward(self, tokens):
             bf16 = lambda t: t.to(torch.bfloat16)
             x = bf16(self.token_embedding(tokens) + self.position_embedding[: tokens.shape[-1]])
@@ -117,6 +151,11 @@ def run_arm(arm: str, steps: int, layers: int, batch: int, sequence: int) -> dic
     torch.manual_seed(20260827)
     model = build_model(torch, package.attnres, layout, layers, width, heads, ffn, vocab,
                         sequence).to(device)
+    staged = layout == "accumulate"
+    if staged:
+        from attnres.accumulate import attnres_accumulate
+        buffers = [torch.zeros(batch, sequence, width, device=device, dtype=torch.bfloat16)
+                   for _ in range(2 * layers + 1)]
     optimizer = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95),
                                   weight_decay=0.1, fused=True, capturable=True)
     tokens = torch.randint(vocab, (batch, sequence), device=device)
@@ -125,10 +164,20 @@ def run_arm(arm: str, steps: int, layers: int, batch: int, sequence: int) -> dic
 
     def step():
         optimizer.zero_grad(set_to_none=False)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            logits = model(tokens)
-        loss = F.cross_entropy(logits.float().view(-1, vocab), targets.view(-1))
-        loss.backward()
+        if not staged:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = model(tokens)
+            loss = F.cross_entropy(logits.float().view(-1, vocab), targets.view(-1))
+            loss.backward()
+        else:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits, attached, first_input = model.forward_staged(tokens, attnres_accumulate, buffers)
+            loss = F.cross_entropy(logits.float().view(-1, vocab), targets.view(-1))
+            loss.backward()                       # LM head and the last read: fills every buffer
+            for index in range(len(attached) - 1, 0, -1):
+                attached[index].backward(buffers[index])   # its reads have all run by now
+            buffers[0] += first_input.grad        # the first attention consumed the embedding directly
+            attached[0].backward(buffers[0])
         optimizer.step()
         loss_buffer.copy_(loss.detach())
 

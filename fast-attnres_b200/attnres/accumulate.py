@@ -54,7 +54,7 @@ def _check_buffers(buffers, shapes, device) -> None:
 
 class _AccumulatingRead(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, query, eps, scale, packed, buffers, *sources):
+    def forward(ctx, query, eps, scale, packed, buffers, overwrite, *sources):
         from . import _ops
         if packed:
             kept, ptrs, rs, fs = _ops._packed_table(sources[0])
@@ -68,6 +68,7 @@ class _AccumulatingRead(torch.autograd.Function):
                                                          scale, keep_residual=True)
         ctx.save_for_backward(query, logits, stats, out, residual, *sources)
         ctx.eps, ctx.scale, ctx.packed, ctx.buffers = eps, scale, packed, buffers
+        ctx.overwrite = overwrite
         ctx.set_materialize_grads(False)
         return out
 
@@ -75,7 +76,7 @@ class _AccumulatingRead(torch.autograd.Function):
     def backward(ctx, grad_output):
         from . import _ops
         count = len(ctx.saved_tensors) - 5
-        nothing = (None,) * (5 + count)
+        nothing = (None,) * (6 + count)
         if grad_output is None:
             return nothing
         query, logits, stats, out, residual, *sources = ctx.saved_tensors
@@ -93,13 +94,16 @@ class _AccumulatingRead(torch.autograd.Function):
         grad_query = _ops._run_backward(kept, ptrs, rs, fs, shape, query, grad_output, logits, stats,
                                         out, residual, ctx.eps, ctx.scale, grad_ptrs,
                                         bool(ctx.needs_input_grad[0]),
-                                        extra_flags=_native.FLAG_ACCUMULATE_DV)
+                                        extra_flags=0 if ctx.overwrite else _native.FLAG_ACCUMULATE_DV)
         return (grad_query, *nothing[1:])
 
 
 def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float = DEFAULT_EPS,
-                       scale: float = 1.0) -> torch.Tensor:
+                       scale: float = 1.0, overwrite: bool = False) -> torch.Tensor:
     """``attnres(values, query)`` whose backward adds dV into ``grad_buffers`` in place.
+
+    ``overwrite=True`` makes the backward of THIS call store its gradients instead of adding
+    them: for the read whose backward runs first in a step, so the buffers need no zeroing.
 
     ``values`` packed ``[S, ..., D]``: ``grad_buffers`` is one contiguous BF16 tensor of the
     same shape.  ``values`` a list/tuple of ``[..., D]`` sources: ``grad_buffers`` is a list of
@@ -113,7 +117,8 @@ def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float 
         if not isinstance(grad_buffers, torch.Tensor):
             raise TypeError("a packed call takes one packed gradient buffer")
         _check_buffers([grad_buffers], [values.shape], values.device)
-        return _AccumulatingRead.apply(query, float(eps), float(scale), True, [grad_buffers], values)
+        return _AccumulatingRead.apply(query, float(eps), float(scale), True, [grad_buffers],
+                                       bool(overwrite), values)
     sources = check_sources(values, query, eps, scale)
     if not sources[0].is_cuda:
         raise RuntimeError("attnres requires CUDA tensors")
@@ -121,7 +126,7 @@ def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float 
         raise TypeError("a list call takes a list of gradient buffers")
     _check_buffers(list(grad_buffers), [s.shape for s in sources], sources[0].device)
     return _AccumulatingRead.apply(query, float(eps), float(scale), False, list(grad_buffers),
-                                   *sources)
+                                   bool(overwrite), *sources)
 
 
 __all__ = ["attnres_accumulate"]

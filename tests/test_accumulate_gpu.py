@@ -108,3 +108,23 @@ def test_c_abi_accumulate_flag_needs_gradient_rows():
                                        0x6000, 16, 1, 0x4000, 0x5000, None, None, None, None,
                                        0x7000, 4, 0x8000, None, _native.FLAG_ACCUMULATE_DV, None)
     assert status == 1
+
+
+@pytest.mark.parametrize("shape", [(9, 400, 2048, 2048), (3, 200, 1024, 256), (5, 9, 3000, 257)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_overwrite_makes_the_first_read_store_instead_of_add(shape):
+    """`overwrite=True` for the read whose backward runs first: no zeroing of the buffers."""
+    from attnres.accumulate import attnres_accumulate
+    torch.manual_seed(3)
+    s, n, d, r = shape
+    values = torch.randn(s, n, d, device="cuda", dtype=BF16)
+    buffers = [torch.full((n, d), float("nan"), device="cuda", dtype=BF16) for _ in range(s)]
+    expected = torch.zeros(s, n, d, device="cuda", dtype=torch.float32)
+    for index in range(2):
+        query = (torch.randn(r, device="cuda", dtype=BF16) * 0.1).requires_grad_()
+        upstream = torch.randn(n, d, device="cuda", dtype=BF16)
+        out = attnres_accumulate(tuple(values.unbind(0)), query, buffers, scale=r ** -0.5,
+                                 overwrite=index == 0)
+        out.backward(upstream)
+        expected += ao.oracle_with_grads(values, query.detach(), upstream, scale=r ** -0.5)[1].float()
+    torch.testing.assert_close(torch.stack(buffers).float(), expected, **TOL)
