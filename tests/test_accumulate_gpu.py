@@ -128,3 +128,31 @@ def test_overwrite_makes_the_first_read_store_instead_of_add(shape):
         out.backward(upstream)
         expected += ao.oracle_with_grads(values, query.detach(), upstream, scale=r ** -0.5)[1].float()
     torch.testing.assert_close(torch.stack(buffers).float(), expected, **TOL)
+
+
+@pytest.mark.parametrize("shape", [(6, 130, 2048, 2048), (4, 50, 264, 72)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_accumulate_reads_strided_sources_and_stays_inside_its_buffers(shape):
+    """Sources that are column slices of wider producers (row stride > D) and gradient buffers
+    carved out of one poisoned allocation: the bands between and around them stay untouched."""
+    from attnres.accumulate import attnres_accumulate
+    torch.manual_seed(9)
+    s, n, d, r = shape
+    producers = [torch.randn(n, d + 8, device="cuda", dtype=BF16) for _ in range(s)]
+    sources = [p[:, :d] for p in producers]
+    pad = 128
+    whole = torch.full((s * (n * d + pad) + pad,), -3.0, device="cuda", dtype=BF16)
+    buffers = [whole[pad + i * (n * d + pad): pad + i * (n * d + pad) + n * d].view(n, d)
+               for i in range(s)]
+    for buffer in buffers:
+        buffer.zero_()
+    query = (torch.randn(r, device="cuda", dtype=BF16) * 0.1).requires_grad_()
+    upstream = torch.randn(n, d, device="cuda", dtype=BF16)
+    attnres_accumulate(sources, query, buffers, scale=0.25).backward(upstream)
+    values = torch.stack([x.contiguous() for x in sources])
+    _, e_dv, e_dq = ao.oracle_with_grads(values, query.detach(), upstream, scale=0.25)
+    torch.testing.assert_close(torch.stack(buffers), e_dv, **TOL)
+    torch.testing.assert_close(query.grad, e_dq, **TOL)
+    for i in range(s + 1):
+        band = whole[i * (n * d + pad): i * (n * d + pad) + pad]
+        assert bool((band == -3.0).all()), f"band {i} was written"
