@@ -382,7 +382,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if args.strong and world > 1 else "weak",
+        "vs_baseline": None,
         "dtype": "bf16 storage / fp32 arithmetic", "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "cells": len(cells),
                    "layout": "packed", "parallelism": f"position-sharded x{world}",
@@ -648,6 +649,9 @@ def main() -> None:
                         help="--cell: also time the backward that adds into running gradient buffers")
     parser.add_argument("--two-pass", action="store_true",
                         help="--cell: never save the output residual (staged backward)")
+    parser.add_argument("--strong", action="store_true",
+                        help="N > 1: split the 16 384 rows of every cell over the ranks (strong "
+                             "scaling) instead of giving every rank its own 16 384 (the default)")
     args = parser.parse_args()
     if args.cell is not None:
         run_single_cell(args)
@@ -662,6 +666,10 @@ def main() -> None:
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU fallback")
+    if args.strong and world > 1:
+        # every rank takes an equal share of the rows (16 384 is a multiple of 2, 4 and 8)
+        global ROWS
+        ROWS = ROWS // world
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
