@@ -631,6 +631,7 @@ def run_single_cell(args) -> None:
 
 
 def main() -> None:
+    global ROWS
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
@@ -668,7 +669,6 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU fallback")
     if args.strong and world > 1:
         # every rank takes an equal share of the rows (16 384 is a multiple of 2, 4 and 8)
-        global ROWS
         ROWS = ROWS // world
     if world > 1:
         import torch.distributed as dist
