@@ -818,3 +818,22 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "LIBRARY_PATH", tmp_path / "absent.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _native.load()
+
+
+def test_in_place_update_of_a_saved_output_is_refused_not_miscomputed():
+    """Where the one-pass backward keeps the output, an in-place update of it between forward
+    and backward must raise (autograd's version check), never give gradients of stale data."""
+    from attnres import _native, attnres
+    torch.manual_seed(2)
+    shape = (9, 64, 2048, 2048)
+    assert _native.wants_output_residual(shape[0], shape[2], shape[3])
+    values = torch.randn(shape[0], shape[1], shape[2], device="cuda", dtype=BF16, requires_grad=True)
+    query = (torch.randn(shape[3], device="cuda", dtype=BF16) * 0.02).requires_grad_()
+    out = attnres(values, query)
+    out.add_(1.0)
+    with pytest.raises(RuntimeError, match="inplace"):
+        out.sum().backward()
+    # the out-of-place form is fine
+    out = attnres(values, query)
+    (out + 1.0).sum().backward()
+    assert values.grad is not None and torch.isfinite(values.grad).all()
