@@ -3,6 +3,7 @@
     python baseline/compare_triton.py                 # both arms, prints a table and JSON
     python baseline/compare_triton.py --arm ours      # one arm (one JSON line)
     python baseline/compare_triton.py --arm triton
+    python baseline/compare_triton.py --abba          # A B B A process order, paired ratio + CI
 
 The reference package is expected under ``baseline/_ref`` (installed offline with
 ``pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <reference>``;
@@ -13,7 +14,11 @@ Protocol (identical for both arms, through each package's public ``attnres()`` +
 the BASELINE config-2 sweep (packed values [S, 16384, D], R = D) and the config-3 shape
 (S=16, D=4096, R=1024); forward+backward of a cell are captured together in one CUDA graph
 after eager warm-up (which also lets Triton autotune), a 256 MB buffer is rewritten between
-replays to evict L2, and the median of the replays is reported.  Errors are measured against
+replays to evict L2, and the median of the replays is reported.  With ``--abba`` the arms run in
+the order Triton, ours, ours, Triton (the ABBA order of the reference's own harness,
+benchmarks/statistics.py:87-211, across processes here because both packages are named
+``attnres``); the replays of an arm's two runs are pooled and the speed-up is the ratio of the
+medians with a 95 % bootstrap interval (2 000 resamples of the replays, fixed seed).  Errors are measured against
 the oracle (``oracle/attnres_oracle.py``) on the device at 2 048 rows: ``max_abs`` and
 ``relative_l2`` exactly as the reference defines them (validation/comparison.py:9-12).
 """
@@ -96,7 +101,7 @@ def run_arm(arm: str, steps: int, cells) -> dict:
         times = sorted(times[2:])
         ms = times[len(times) // 2]
         bytes_moved = ROWS * (6 * sources * width + 4 * width)
-        results.append({"S": sources, "D": width, "R": rank, "fwd_bwd_ms": ms,
+        results.append({"S": sources, "D": width, "R": rank, "fwd_bwd_ms": ms, "samples_ms": times,
                         "tokens_per_s": ROWS / (ms * 1e-3), "gbs": bytes_moved / ms / 1e6,
                         "errors": errors})
         del graph, kept, values, query, upstream
@@ -111,6 +116,9 @@ def main() -> None:
     parser.add_argument("--arm", choices=("ours", "triton", "both"), default="both")
     parser.add_argument("--steps", type=int, default=7)
     parser.add_argument("--cells", default=None, help="subset, e.g. '9,2048,2048;16,4096,1024'")
+    parser.add_argument("--abba", action="store_true",
+                        help="run Triton, ours, ours, Triton and report paired ratios with a "
+                             "bootstrap confidence interval")
     args = parser.parse_args()
     cells = CELLS if args.cells is None else [tuple(int(x) for x in c.split(","))
                                               for c in args.cells.split(";")]
@@ -120,15 +128,35 @@ def main() -> None:
     if not (ROOT / "baseline" / "_ref" / "attnres").exists():
         print(json.dumps({"unavailable": "baseline/_ref holds no reference install"}))
         return
-    arms = {}
-    for arm in ("triton", "ours"):
+    arms, runs = {}, []
+    for arm in (("triton", "ours", "ours", "triton") if args.abba else ("triton", "ours")):
         command = [sys.executable, str(Path(__file__).resolve()), "--arm", arm, "--steps",
                    str(args.steps)] + (["--cells", args.cells] if args.cells else [])
         done = subprocess.run(command, capture_output=True, text=True)
         if done.returncode != 0:
             print(json.dumps({"arm": arm, "failed": done.stderr[-2000:]}))
             return
-        arms[arm] = json.loads(done.stdout.strip().splitlines()[-1])
+        runs.append((arm, json.loads(done.stdout.strip().splitlines()[-1])))
+        arms.setdefault(arm, runs[-1][1])
+    if args.abba:
+        import numpy as np
+        generator = np.random.default_rng(20260827)
+        print("| S | D | R | Triton ms | ours ms | speed-up | 95 % interval |")
+        print("|---|---|---|---|---|---|---|")
+        for index, cell in enumerate(arms["triton"]["cells"]):
+            pooled = {arm: np.array([x for name, run in runs if name == arm
+                                     for x in run["cells"][index]["samples_ms"]])
+                      for arm in ("triton", "ours")}
+            ratio = np.median(pooled["triton"]) / np.median(pooled["ours"])
+            draws = [np.median(generator.choice(pooled["triton"], pooled["triton"].size)) /
+                     np.median(generator.choice(pooled["ours"], pooled["ours"].size))
+                     for _ in range(2000)]
+            low, high = np.percentile(draws, [2.5, 97.5])
+            print(f"| {cell['S']} | {cell['D']} | {cell['R']} | {np.median(pooled['triton']):.3f} | "
+                  f"{np.median(pooled['ours']):.3f} | {ratio:.2f}x | {low:.2f}x – {high:.2f}x |")
+        print(json.dumps({"order": [name for name, _ in runs], "runs": [run for _, run in runs]}),
+              flush=True)
+        return
     print("| S | D | R | Triton ms | ours ms | speed-up | out rel-L2 (T / ours) | dV rel-L2 (T / ours) "
           "| dq rel-L2 (T / ours) | dq max-abs (T / ours) |")
     print("|---|---|---|---|---|---|---|---|---|---|")
