@@ -1,16 +1,14 @@
-"""AttnRes read for B200: BF16 values, sliced tail keys, sm_100a CUDA kernels.
+"""AttnRes read for B200: BF16 storage, sliced tail keys, hand-written sm_100a kernels.
 
-Drop-in for the public surface of the reference package
-(src/attnres/__init__.py:8-15): ``attnres``, ``LearnedQuery``, ``__version__``.
+The importable surface is the reference package's (src/attnres/__init__.py:8-15):
+``attnres``, ``LearnedQuery`` and ``__version__``; ``python -m attnres.info`` reports the
+state of the CUDA library.  ``attnres.accumulate`` and ``attnres.parallel`` are additions.
 """
+from . import api as _api
+from . import modules as _modules
 
 __version__ = "0.1.0"
+attnres = _api.attnres
+LearnedQuery = _modules.LearnedQuery
 
-from .api import attnres
-from .modules import LearnedQuery
-
-__all__ = [
-    "LearnedQuery",
-    "__version__",
-    "attnres",
-]
+__all__ = ["LearnedQuery", "__version__", "attnres"]

@@ -1,8 +1,13 @@
-"""Argument validation shared by the packed and source-list entry points.
+"""Argument checks of the packed and the source-list entry points, and the row layout of a
+source.
 
-Same checks, exception types and order as the reference
-(src/attnres/_sources.py:16-93 and src/attnres/api.py:9-27); nothing here
-copies, stacks or makes a tensor contiguous.
+A call is refused with the exception TYPE the reference raises for the same mistake, and when
+several things are wrong the same one is reported first (src/attnres/api.py:9-27 for a packed
+tensor, src/attnres/_sources.py:16-93 for a list): wrong container or element types and wrong
+dtypes or devices are ``TypeError``; ranks, extents, the S <= 129 / D <= 8192 / R <= D envelope
+and non-finite scalars are ``ValueError``; CPU tensors are ``RuntimeError`` and are reported
+last.  Each entry point is an ordered table of (condition that must hold, exception, message);
+the first condition that fails decides.  Nothing here copies, stacks or re-lays-out a tensor.
 """
 from __future__ import annotations
 
@@ -17,31 +22,41 @@ MAX_WIDTH = 8192
 _BF16 = torch.bfloat16
 
 
+def _first_failure(rules) -> None:
+    """Raise for the first rule whose condition does not hold; conditions are evaluated
+    lazily and in order, so a later one may rely on the earlier ones."""
+    for holds, kind, message in rules:
+        if not holds():
+            raise kind(message)
+
+
 def check_scalar(value, name: str, *, positive: bool = False) -> None:
-    """Real, finite (and optionally positive) Python scalars only; bool is refused."""
-    if isinstance(value, bool) or not isinstance(value, Real):
-        raise TypeError(f"{name} must be a real scalar")
-    number = float(value)
-    if not math.isfinite(number) or (positive and number <= 0.0):
-        raise ValueError(f"{name} must be {'finite and positive' if positive else 'finite'}")
+    """``eps`` / ``scale``: a real Python number (not a bool, string or tensor), finite, and
+    for ``positive=True`` greater than zero."""
+    wanted = "finite and positive" if positive else "finite"
+    _first_failure((
+        (lambda: isinstance(value, Real) and not isinstance(value, bool), TypeError,
+         f"{name} must be a real scalar"),
+        (lambda: math.isfinite(float(value)), ValueError, f"{name} must be {wanted}"),
+        (lambda: not positive or float(value) > 0.0, ValueError, f"{name} must be {wanted}"),
+    ))
 
 
 def check_packed(values: torch.Tensor, query, eps, scale) -> None:
-    """Validation of a packed ``[S, ..., D]`` call (src/attnres/api.py:9-27)."""
-    if not isinstance(query, torch.Tensor):
-        raise TypeError("query must be a tensor")
-    if values.ndim < 2 or query.ndim != 1:
-        raise ValueError("expected values [S,...,D] and query [R]")
-    if not 1 <= values.shape[0] <= MAX_SOURCES or not 1 <= values.shape[-1] <= MAX_WIDTH:
-        raise ValueError(f"supported envelope is 1<=S<={MAX_SOURCES} and 1<=D<={MAX_WIDTH}")
-    if any(size < 1 for size in values.shape) or not 1 <= query.numel() <= values.shape[-1]:
-        raise ValueError("dimensions must be positive and 1<=R<=D")
-    if values.dtype != _BF16:
-        raise TypeError("values must use BF16 storage")
-    if query.dtype != _BF16:
-        raise TypeError("query must use BF16 storage")
-    if query.device != values.device:
-        raise TypeError("query must be on the values device")
+    """A packed call: ``values`` is ``[S, ..., D]``, ``query`` is ``[R]``."""
+    envelope = f"supported envelope is 1<=S<={MAX_SOURCES} and 1<=D<={MAX_WIDTH}"
+    _first_failure((
+        (lambda: isinstance(query, torch.Tensor), TypeError, "query must be a tensor"),
+        (lambda: values.ndim >= 2 and query.ndim == 1, ValueError,
+         "expected values [S,...,D] and query [R]"),
+        (lambda: 1 <= values.shape[0] <= MAX_SOURCES and 1 <= values.shape[-1] <= MAX_WIDTH,
+         ValueError, envelope),
+        (lambda: min(values.shape) >= 1 and 1 <= query.numel() <= values.shape[-1], ValueError,
+         "dimensions must be positive and 1<=R<=D"),
+        (lambda: values.dtype == _BF16, TypeError, "values must use BF16 storage"),
+        (lambda: query.dtype == _BF16, TypeError, "query must use BF16 storage"),
+        (lambda: query.device == values.device, TypeError, "query must be on the values device"),
+    ))
     check_scalar(eps, "eps", positive=True)
     check_scalar(scale, "scale")
     if not values.is_cuda:
@@ -49,43 +64,39 @@ def check_packed(values: torch.Tensor, query, eps, scale) -> None:
 
 
 def check_sources(values, query, eps, scale) -> tuple[torch.Tensor, ...]:
-    """Validation of a list/tuple call; returns the sources as a tuple, untouched
-    (src/attnres/_sources.py:37-93)."""
-    if not isinstance(query, torch.Tensor):
-        raise TypeError("query must be a tensor")
-    if query.ndim != 1:
-        raise ValueError("query must have 1 dimensions")
-    if any(int(size) < 1 for size in query.shape):
-        raise ValueError("query dimensions must be positive")
-    if query.dtype != _BF16:
-        raise TypeError("query must use BF16 storage")
-    if not isinstance(values, (list, tuple)):
-        raise TypeError("values must be a tensor or a list/tuple of tensors")
+    """A list/tuple call: S tensors ``[..., D]`` of one shape, dtype and device.  Returns the
+    sources as a tuple of the very same tensor objects."""
+    _first_failure((
+        (lambda: isinstance(query, torch.Tensor), TypeError, "query must be a tensor"),
+        (lambda: query.ndim == 1, ValueError, "query must have 1 dimensions"),
+        (lambda: query.numel() >= 1, ValueError, "query dimensions must be positive"),
+        (lambda: query.dtype == _BF16, TypeError, "query must use BF16 storage"),
+        (lambda: isinstance(values, (list, tuple)), TypeError,
+         "values must be a tensor or a list/tuple of tensors"),
+        (lambda: 1 <= len(values) <= MAX_SOURCES, ValueError,
+         f"supported source envelope is 1<=S<={MAX_SOURCES}"),
+        (lambda: all(isinstance(item, torch.Tensor) for item in values), TypeError,
+         "values must contain only tensors"),
+    ))
     sources = tuple(values)
-    if not 1 <= len(sources) <= MAX_SOURCES:
-        raise ValueError(f"supported source envelope is 1<=S<={MAX_SOURCES}")
-    if any(not isinstance(source, torch.Tensor) for source in sources):
-        raise TypeError("values must contain only tensors")
-    first = sources[0]
-    if first.ndim < 1:
-        raise ValueError("each source must have shape [...,D]")
-    if any(int(size) < 1 for size in first.shape):
-        raise ValueError("source dimensions must be positive")
-    width = int(first.shape[-1])
-    if not 1 <= width <= MAX_WIDTH:
-        raise ValueError(f"supported value envelope is 1<=D<={MAX_WIDTH}")
-    if first.dtype != _BF16:
-        raise TypeError("values must use BF16 storage")
-    if query.device != first.device:
-        raise TypeError("query must be on the values device")
-    for index, source in enumerate(sources):
-        if source.ndim < 1:
-            raise ValueError(f"source {index} must have shape [...,D]")
-        if tuple(source.shape) != tuple(first.shape):
-            raise ValueError("all source tensors must have the same logical shape")
-        if source.dtype != first.dtype or source.device != first.device:
-            raise TypeError("all source tensors must match the first source dtype/device")
-    if not 1 <= int(query.shape[-1]) <= width:
+    head = sources[0]
+    _first_failure((
+        (lambda: head.ndim >= 1, ValueError, "each source must have shape [...,D]"),
+        (lambda: min(head.shape) >= 1, ValueError, "source dimensions must be positive"),
+        (lambda: head.shape[-1] <= MAX_WIDTH, ValueError,
+         f"supported value envelope is 1<=D<={MAX_WIDTH}"),
+        (lambda: head.dtype == _BF16, TypeError, "values must use BF16 storage"),
+        (lambda: query.device == head.device, TypeError, "query must be on the values device"),
+    ))
+    for position, item in enumerate(sources):
+        _first_failure((
+            (lambda: item.ndim >= 1, ValueError, f"source {position} must have shape [...,D]"),
+            (lambda: item.shape == head.shape, ValueError,
+             "all source tensors must have the same logical shape"),
+            (lambda: item.dtype == head.dtype and item.device == head.device, TypeError,
+             "all source tensors must match the first source dtype/device"),
+        ))
+    if query.numel() > head.shape[-1]:
         raise ValueError("query rank must satisfy 1<=R<=D")
     check_scalar(eps, "eps", positive=True)
     check_scalar(scale, "scale")

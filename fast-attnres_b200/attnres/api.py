@@ -1,40 +1,44 @@
-"""Public functional entry point (same contract as src/attnres/api.py:30-62)."""
+"""``attnres(values, query, *, eps, scale)``: the one public function.
+
+Signature, defaults, accepted containers and the exceptions raised for bad arguments are those
+of the reference's entry point (src/attnres/api.py:30-62); the work is done by the sm_100a
+library behind ``attnres_b200::read_packed_forward`` / ``read_sources_forward``.
+"""
 from __future__ import annotations
 
+from typing import Sequence, Union
+
 import torch
-from torch import Tensor
 
-from ._sources import DEFAULT_EPS, check_packed, check_sources
+from . import _sources
+
+Values = Union[torch.Tensor, Sequence[torch.Tensor]]
 
 
-def attnres(
-    values: Tensor | list[Tensor] | tuple[Tensor, ...],
-    query: Tensor,
-    *,
-    eps: float = DEFAULT_EPS,
-    scale: float = 1.0,
-) -> Tensor:
-    """Mix source values with a static query over implicit tail keys.
+def attnres(values: Values, query: torch.Tensor, *, eps: float = _sources.DEFAULT_EPS,
+            scale: float = 1.0) -> torch.Tensor:
+    """Softmax-over-sources read of ``values`` with the static ``query``.
 
-    ``values`` is a packed ``[S, ..., D]`` tensor or an ordered list/tuple of
-    ``S`` tensors ``[..., D]``; ``query`` is ``[R]`` with ``1 <= R <= D``.  The
-    key of a source is its final ``R`` features, RMS-normalised; the softmax runs
-    over the source axis independently at every position and the result keeps
-    the full width ``D``.  Inputs and outputs are CUDA BF16 tensors; reductions
-    are FP32.  First-order gradients flow to every source and to the query.
+    ``values``: one packed tensor ``[S, ..., D]``, or a list / tuple of ``S`` tensors
+    ``[..., D]`` (any strides; nothing is stacked or copied unless a source's leading axes cannot
+    be walked with one stride).  ``query``: ``[R]``, ``1 <= R <= D``.  The key of source ``s`` at
+    a position is the RMS-normalised tail ``v_s[..., D-R:]`` (``eps`` inside the square root);
+    its logit is ``scale`` times the key's dot product with ``query``; the result is the
+    softmax-weighted sum of the full-width sources, one softmax per position.  ``R == D`` is the
+    standard form, ``R < D`` the sliced low-rank one.
+
+    Storage is BF16 on a CUDA device, arithmetic FP32; the result is BF16 ``[..., D]`` and
+    carries first-order gradients to every source and to ``query``.
     """
-    if isinstance(values, torch.Tensor):
-        check_packed(values, query, eps, scale)
-        from ._ops import packed_read  # the CUDA library loads on first GPU use only
-
-        return packed_read(values, query, eps, scale)
-
-    sources = check_sources(values, query, eps, scale)
-    if not sources[0].is_cuda:
+    if torch.is_tensor(values):
+        _sources.check_packed(values, query, eps, scale)
+        from . import _ops  # deferred: loading the CUDA library is not needed to reject a call
+        return _ops.packed_read(values, query, eps, scale)
+    listed = _sources.check_sources(values, query, eps, scale)
+    if listed[0].device.type != "cuda":
         raise RuntimeError("attnres requires CUDA tensors")
-    from ._ops import sources_read
-
-    return sources_read(sources, query, eps, scale)
+    from . import _ops
+    return _ops.sources_read(listed, query, eps, scale)
 
 
 __all__ = ["attnres"]

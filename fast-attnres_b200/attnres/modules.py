@@ -1,43 +1,52 @@
-"""Trainable query parameter for the AttnRes read.
+"""``LearnedQuery``: the trainable ``[rank]`` vector a read is queried with.
 
-Mirrors src/attnres/modules.py:22-38: a BF16 ``[rank]`` parameter drawn from
-N(0, init_std); ``forward()`` always hands the operator a BF16 tensor, so a
-module cast to FP32 still trains (FP32 parameter, BF16 query, FP32 gradient).
+Behaviour follows src/attnres/modules.py:22-38 of the reference: the parameter is created in
+BF16 from N(0, init_std); calling the module returns the parameter as BF16 whatever dtype the
+module was later cast to, so an FP32 master copy trains through a BF16 query and receives an
+FP32 gradient.  Bad arguments raise the same exception types as the reference
+(tests/test_info.py:27-38, tests/test_api.py of the reference).
 """
 from __future__ import annotations
 
 import math
-import operator
+from numbers import Integral
 
 import torch
-from torch import nn
 
 
-def _as_index(value, name: str) -> int:
-    if isinstance(value, bool):
-        raise TypeError(f"{name} must be an integer")
+def _length(rank) -> int:
+    """``rank`` as a positive int; integer-like objects (``__index__``) are accepted, bools and
+    floats are not."""
+    if isinstance(rank, bool) or not (isinstance(rank, Integral) or hasattr(rank, "__index__")):
+        raise TypeError("rank must be an integer")
     try:
-        return operator.index(value)
+        length = rank.__index__()
     except TypeError as error:
-        raise TypeError(f"{name} must be an integer") from error
+        raise TypeError("rank must be an integer") from error
+    if length <= 0:
+        raise ValueError("rank must be positive")
+    return length
 
 
-class LearnedQuery(nn.Module):
-    """A static trainable query vector of length ``rank``."""
+def _spread(init_std) -> float:
+    value = float(init_std)
+    if math.isnan(value) or math.isinf(value) or value <= 0.0:
+        raise ValueError("init_std must be finite and positive")
+    return value
+
+
+class LearnedQuery(torch.nn.Module):
+    """Holds one query vector of ``rank`` entries and hands it out in BF16."""
 
     def __init__(self, rank: int, *, init_std: float = 0.02) -> None:
         super().__init__()
-        rank = _as_index(rank, "rank")
-        init_std = float(init_std)
-        if rank < 1:
-            raise ValueError("rank must be positive")
-        if not math.isfinite(init_std) or init_std <= 0:
-            raise ValueError("init_std must be finite and positive")
-        self.query = nn.Parameter(torch.empty(rank, dtype=torch.bfloat16))
-        nn.init.normal_(self.query, mean=0.0, std=init_std)
+        length, spread = _length(rank), _spread(init_std)
+        start = torch.empty(length, dtype=torch.bfloat16).normal_(mean=0.0, std=spread)
+        self.query = torch.nn.Parameter(start)
 
     def forward(self) -> torch.Tensor:
-        return self.query.to(dtype=torch.bfloat16)
+        # ``.to`` is the identity for a BF16 parameter and a differentiable cast otherwise
+        return self.query.to(torch.bfloat16)
 
 
 __all__ = ["LearnedQuery"]
