@@ -11,7 +11,7 @@ the directory is git-ignored).  Both packages are called ``attnres``, so every a
 its own process with only its own package on ``sys.path``.
 
 Protocol (identical for both arms, through each package's public ``attnres()`` + autograd):
-the BASELINE config-2 sweep (packed values [S, 16384, D], R = D) and the config-3 shape
+the reference's operator sweep (packed values [S, 16384, D], R = D) and its sliced low-rank shape
 (S=16, D=4096, R=1024); forward+backward of a cell are captured together in one CUDA graph
 after eager warm-up (which also lets Triton autotune), a 256 MB buffer is rewritten between
 replays to evict L2, and the median of the replays is reported.  With ``--abba`` the arms run in

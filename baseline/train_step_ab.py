@@ -1,4 +1,4 @@
-"""24-layer Full-schedule training step (BASELINE config 4): this library vs the reference's
+"""24-layer Full-schedule training step (the reference's 24-layer model benchmark): this library vs the reference's
 Triton kernels on the same GPU.
 
     python baseline/train_step_ab.py                       # every arm, one after the other

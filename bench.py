@@ -2,7 +2,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 2, "standard full-rank operator sweep"): packed BF16
+Workload (the reference's "standard full-rank operator sweep", its second benchmark
+configuration): packed BF16
 values [S, 16384, D] ~ N(0,1) for S in {2,5,9,17,25,49} x D in {1024,2048,4096},
 query [D] ~ N(0,0.02), R = D, upstream gradient ~ N(0,1).  One STEP is one
 forward and one backward of every one of the 18 cells: all forwards first, then

@@ -39,7 +39,9 @@ def bits(tensor: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    reference_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/fast-attnres")
+    reference_root = Path(sys.argv[1])
     spec = importlib.util.spec_from_file_location(
         "reference_validation_oracle", reference_root / "validation" / "oracle.py")
     module = importlib.util.module_from_spec(spec)
@@ -54,7 +56,7 @@ def main() -> None:
         query = (torch.randn(R) * query_std).to(torch.bfloat16).requires_grad_()
         out = reference_oracle(values, query, eps=eps, scale=scale)
         if loss == "square_mean":
-            # BASELINE config 1: loss = output.square().mean(); the upstream gradient
+            # the reference's CPU oracle run: loss = output.square().mean(); the upstream gradient
             # autograd hands the operator is d loss / d out in BF16.
             total = out.square().mean()
             upstream, = torch.autograd.grad(total, out, retain_graph=True)

@@ -4,7 +4,7 @@ Tolerance: the reference's protocol, rtol = atol = 0.05 on BF16 outputs, value
 gradients and query gradients (validation/protocol.json:12-15), plus tighter
 relative-L2 bounds stated per test.  Shapes are the reference's envelope
 (validation/protocol.json:16-112, tests/test_cuda.py:27-31, :296-305 and
-tests/test_bf16_packed_kernels.py of the reference) and BASELINE's configs.
+tests/test_bf16_packed_kernels.py of the reference) and the shapes of its benchmark configurations.
 """
 import gc
 import weakref
@@ -120,7 +120,7 @@ def test_eps_and_scale_reach_the_kernels(eps, scale, family):
     _single((5, 9, 264, 72), eps=eps, scale=scale, strided=False)
 
 
-# ------------------------------------------------------------------ BASELINE shapes (reduced rows)
+# ------------------------------------------------------------------ benchmark shapes (reduced rows)
 
 SWEEP = [(s, d) for d in (1024, 2048, 4096) for s in (2, 5, 9, 17, 25, 49)]
 
@@ -128,21 +128,24 @@ SWEEP = [(s, d) for d in (1024, 2048, 4096) for s in (2, 5, 9, 17, 25, 49)]
 @pytest.mark.parametrize("as_list", [False, True], ids=["packed", "list"])
 @pytest.mark.parametrize("sources,width", SWEEP)
 def test_operator_sweep_shapes_reduced_rows(sources, width, as_list, family):
-    """BASELINE config 2 at N = 384 rows: values ~N(0,1), query ~N(0,0.02), R = D."""
+    """The operator sweep (benchmark configuration 2) at N = 384 rows: values ~N(0,1), query
+    ~N(0,0.02), R = D."""
     torch.manual_seed(20260827 + sources + width)
     _single((sources, 384, width, width), strided=False, as_list=as_list, query_std=0.02)
 
 
 @pytest.mark.parametrize("rank,scale", [(1024, 1 / 32), (4096, 1 / 64)])
 def test_sliced_low_rank_shape_reduced_rows(rank, scale, family):
-    """BASELINE config 3 at N = 512 rows: S = 16, D = 4096, R = 1024 (and R = D)."""
+    """The sliced low-rank shape (benchmark configuration 3) at N = 512 rows: S = 16, D = 4096,
+    R = 1024 (and R = D)."""
     torch.manual_seed(20260903)
     _single((16, 512, 4096, rank), strided=False, scale=scale, query_std=0.02)
 
 
 @pytest.mark.parametrize("sources", [2, 4, 7])
 def test_block_schedule_shape_reduced_rows(sources, family):
-    """BASELINE config 5 read: D = 4096, R = 1024, S <= 7."""
+    """The reads of the D = 4096 Block-schedule model (benchmark configuration 5): R = 1024,
+    S <= 7."""
     torch.manual_seed(20260911)
     _single((sources, 300, 4096, 1024), strided=False, as_list=True, scale=1 / 32, query_std=0.02)
 
@@ -152,7 +155,7 @@ def test_block_schedule_shape_reduced_rows(sources, family):
 @pytest.mark.parametrize("sources,width,rank", [(9, 2048, 2048), (2, 1024, 1024), (17, 4096, 4096),
                                                 (16, 4096, 1024)])
 def test_full_size_rows_against_oracle_and_row_independence(sources, width, rank):
-    """N = 16 384 rows (BASELINE configs 2 and 3).  Checks (a) parity with the oracle
+    """N = 16 384 rows (benchmark configurations 2 and 3).  Checks (a) parity with the oracle
     evaluated on the device, (b) positions are independent: any row block computed alone
     gives the same bits as inside the full call, (c) the output is a convex combination
     of the sources, (d) the query gradient of the whole equals the sum over row blocks."""
