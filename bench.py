@@ -71,16 +71,25 @@ def measured_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def traffic_ratio() -> float | None:
-    """DRAM bytes / algorithmic bytes of the backward kernel from the committed ncu
-    capture (profiles/dram_traffic.json), or None when no capture is recorded."""
+def traffic_ratios() -> dict:
+    """DRAM bytes / algorithmic bytes per backward kernel family ("stream", "stash", "ring")
+    from the committed ncu captures (profiles/dram_traffic.json); empty when none is recorded."""
     path = ROOT / "profiles" / "dram_traffic.json"
     if path.exists():
         try:
-            return float(json.loads(path.read_text())["backward"]["dram_over_algorithmic"])
+            table = json.loads(path.read_text())["backward"]
+            return {name: float(entry["dram_over_algorithmic"]) for name, entry in table.items()
+                    if isinstance(entry, dict) and "dram_over_algorithmic" in entry}
         except Exception:
-            return None
-    return None
+            return {}
+    return {}
+
+
+def backward_family(sources: int, saves_output: bool) -> str:
+    """Which backward kernel the library runs for a cell of the sweep (aligned layout)."""
+    if saves_output:
+        return "stream"
+    return "ring" if sources <= 4 else "stash"
 
 
 class ClockSampler:
@@ -168,9 +177,18 @@ def cpu_oracle_tokens_per_s(rows: int, repeats: int = 1) -> tuple[float, float, 
     return repeats * len(CELLS) * rows / seconds, seconds, torch.get_num_threads()
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU arm runs on rank 0 alone and
+    takes every host core, as it does when launched without torchrun."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args, rank: int) -> None:
     if rank != 0:
         return
+    use_all_host_threads()
     rates, elapsed = [], 0.0
     for _ in range(max(1, min(args.warmup, 2))):  # untimed passes
         cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS)
@@ -207,15 +225,16 @@ class Cell:
                                   generator=generator)
         self.query = (torch.randn(width, device=device, generator=generator) * 0.02).to(torch.bfloat16)
         self.upstream = upstream
-        # Where the library's one-pass backward wants the forward's output and its BF16
+        # Where the library's one-pass backward wants the forward's output and its 16-bit
         # residual, both must survive until the cell's backward: such a cell owns them.
         self.saves_output = _native.wants_output_residual(sources, width, width)
         if self.saves_output:
             self.out = torch.empty(ROWS, width, device=device, dtype=torch.bfloat16)
-            self.residual = torch.empty(ROWS, width, device=device, dtype=torch.bfloat16)
+            self.residual = torch.empty(ROWS, width, device=device, dtype=torch.int16)
         else:
             self.out = out_buffer[:ROWS * width].view(ROWS, width)
             self.residual = None
+        self.family = backward_family(sources, self.saves_output)
         self.grad = grad_buffer[:sources * ROWS * width].view(sources, ROWS, width)
         self.logits = torch.empty(sources, ROWS, device=device, dtype=torch.float32)
         self.stats = torch.empty(2, ROWS, device=device, dtype=torch.float32)
@@ -227,18 +246,21 @@ class Cell:
         self.src_ptrs = [self.values.data_ptr() + s * step for s in range(sources)]
         self.grad_ptrs = [self.grad.data_ptr() + s * step for s in range(sources)]
         self.fwd_bytes, self.bwd_bytes = algorithmic_bytes(sources, ROWS, width)
-        self.fwd_graph = self.bwd_graph = None
+        self.graphs = {}   # rows -> (forward graph, backward graph)
 
-    def forward(self, stream):
+    def forward(self, stream, rows):
+        """The first `rows` positions of the cell (all of them in the weak-scaling step; a
+        1/world share in the strong-scaling one: the row stride of the sources is unchanged,
+        the logits and statistics are laid out for `rows` positions)."""
         from attnres import _native
-        _native.forward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, self.N, self.D,
+        _native.forward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, rows, self.D,
                         self.D, self.query.data_ptr(), 1, 2**-23, 1.0, self.out.data_ptr(), self.D,
                         self.logits.data_ptr(), self.stats.data_ptr(), 0, stream,
                         residual_ptr=self.residual.data_ptr() if self.saves_output else None)
 
-    def backward(self, stream, distributed):
+    def backward(self, stream, rows, distributed):
         from attnres import _native
-        _native.backward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, self.N, self.D,
+        _native.backward(self.src_ptrs, [self.D] * self.S, [1] * self.S, self.S, rows, self.D,
                          self.D, self.query.data_ptr(), 1, 2**-23, 1.0,
                          self.upstream.data_ptr(), self.D, 1,
                          self.logits.data_ptr(), self.stats.data_ptr(),
@@ -249,25 +271,104 @@ class Cell:
                          out_ptr=self.out.data_ptr() if self.saves_output else None,
                          residual_ptr=self.residual.data_ptr() if self.saves_output else None)
 
-    def capture(self, distributed):
+    def capture(self, rows, distributed):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            self.forward(side.cuda_stream)
-            self.backward(side.cuda_stream, distributed)
+            self.forward(side.cuda_stream, rows)
+            self.backward(side.cuda_stream, rows, distributed)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        self.fwd_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.fwd_graph):
-            self.forward(torch.cuda.current_stream().cuda_stream)
-        self.bwd_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.bwd_graph):
-            self.backward(torch.cuda.current_stream().cuda_stream, distributed)
+        fwd_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fwd_graph):
+            self.forward(torch.cuda.current_stream().cuda_stream, rows)
+        bwd_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(bwd_graph):
+            self.backward(torch.cuda.current_stream().cuda_stream, rows, distributed)
+        self.graphs[rows] = (fwd_graph, bwd_graph)
+
+
+def time_sweep(cells, rows, steps, warmup, flat32, flat16, distributed, device, sampler=None):
+    """`warmup` untimed and `steps` timed steps of the sweep at `rows` positions per cell and
+    rank.  Returns (ms per step, max over ranks; per-cell forward ms; per-cell backward ms;
+    this rank's own kernel ms per step; ms per step of the collective and the cast)."""
+    import contextlib
+    import torch.distributed as dist
+
+    def pairs(count):
+        return [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                for _ in range(count)]
+
+    def step(fwd_events=None, bwd_events=None, tail_events=None):
+        for index, cell in enumerate(cells):
+            if fwd_events:
+                fwd_events[index][0].record()
+            cell.graphs[rows][0].replay()
+            if fwd_events:
+                fwd_events[index][1].record()
+        for index in reversed(range(len(cells))):
+            if bwd_events:
+                bwd_events[index][0].record()
+            cells[index].graphs[rows][1].replay()
+            if bwd_events:
+                bwd_events[index][1].record()
+        if distributed:
+            # The host is many launches ahead of the GPU here, so the collective is already
+            # queued when the last backward ends; what it costs is its own kernels and the wait
+            # for the slowest rank.
+            if tail_events:
+                tail_events[0].record()
+            dist.all_reduce(flat32)
+            flat16.copy_(flat32)
+            if tail_events:
+                tail_events[1].record()
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    records = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with (sampler if sampler is not None else contextlib.nullcontext()):
+        start.record()
+        for _ in range(steps):
+            fe, be, te = pairs(len(cells)), pairs(len(cells)), pairs(1)[0]
+            step(fe, be, te)
+            records.append((fe, be, te))
+        stop.record()
+        barrier()
+    total_ms = start.elapsed_time(stop)
+    fwd_ms, bwd_ms, tail_ms = [0.0] * len(cells), [0.0] * len(cells), 0.0
+    for fe, be, te in records:
+        for index in range(len(cells)):
+            fwd_ms[index] += fe[index][0].elapsed_time(fe[index][1]) / steps
+            bwd_ms[index] += be[index][0].elapsed_time(be[index][1]) / steps
+        if distributed:
+            tail_ms += te[0].elapsed_time(te[1]) / steps
+    own_ms = sum(fwd_ms) + sum(bwd_ms)
+    if distributed:
+        worst = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        total_ms = float(worst.item())
+    return total_ms / steps, fwd_ms, bwd_ms, own_ms, tail_ms
+
+
+def gather_floats(value: float, device, world: int) -> list[float]:
+    import torch.distributed as dist
+    if world == 1:
+        return [value]
+    mine = torch.tensor([value], device=device, dtype=torch.float64)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    return [float(t.item()) for t in every]
 
 
 def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
-    import torch.distributed as dist
-    from attnres import _native, attnres
+    from attnres import _native
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     distributed = world > 1
@@ -288,73 +389,57 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     for cell in cells:
         cell.dq32, cell.dq = flat32[offset:offset + cell.D], flat16[offset:offset + cell.D]
         offset += cell.D
+    # Weak scaling (the headline): every rank owns ROWS positions of every cell.  Strong
+    # scaling (a sub-record): the ROWS positions of every cell are split over the ranks.
+    strong_rows = ROWS // world
     for cell in cells:
-        cell.capture(distributed)
+        cell.capture(ROWS, distributed)
+        if distributed:
+            cell.capture(strong_rows, distributed)
     torch.cuda.synchronize()
 
-    def make_events():
-        return [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                for _ in cells]
-
-    def step(fwd_events=None, bwd_events=None):
-        for index, cell in enumerate(cells):
-            if fwd_events:
-                fwd_events[index][0].record()
-            cell.fwd_graph.replay()
-            if fwd_events:
-                fwd_events[index][1].record()
-        for index in reversed(range(len(cells))):
-            cell = cells[index]
-            if bwd_events:
-                bwd_events[index][0].record()
-            cell.bwd_graph.replay()
-            if bwd_events:
-                bwd_events[index][1].record()
-        if distributed:
-            dist.all_reduce(flat32)
-            flat16.copy_(flat32)
-
-    def barrier():
-        if distributed:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    fwd_ms = [0.0] * len(cells)
-    bwd_ms = [0.0] * len(cells)
-    all_events = []
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        start.record()
-        for _ in range(args.steps):
-            fe, be = make_events(), make_events()
-            step(fe, be)
-            all_events.append((fe, be))
-        stop.record()
-        barrier()
-    total_ms = start.elapsed_time(stop)
-    for fe, be in all_events:
-        for index in range(len(cells)):
-            fwd_ms[index] += fe[index][0].elapsed_time(fe[index][1]) / args.steps
-            bwd_ms[index] += be[index][0].elapsed_time(be[index][1]) / args.steps
-    if distributed:
-        worst = torch.tensor([total_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        total_ms = float(worst.item())
-    ms_per_step = total_ms / args.steps
+    clocks = ClockSampler(local_rank)
+    ms_per_step, fwd_ms, bwd_ms, own_ms, tail_ms = time_sweep(
+        cells, ROWS, args.steps, args.warmup, flat32, flat16, distributed, device, clocks)
     tokens_per_step = world * len(cells) * ROWS
     value = tokens_per_step / (ms_per_step * 1e-3)
+    rank_kernel_ms = gather_floats(own_ms, device, world)
+    rank_tail_ms = gather_floats(tail_ms, device, world)
+
+    strong = None
+    if distributed:
+        s_ms, s_fwd, s_bwd, s_own, s_tail = time_sweep(
+            cells, strong_rows, args.steps, args.warmup, flat32, flat16, distributed, device)
+        strong_rank_ms = gather_floats(s_own, device, world)
+        # A cell is called launch-bound when its two passes take more than twice what its
+        # bytes need at the measured copy bandwidth (fixed launch, ramp-up and tail costs
+        # dominate a 1/world share of a small cell).
+        peak_now, _ = measured_peak_gbs()
+        slow = []
+        for cell, f, b in zip(cells, s_fwd, s_bwd):
+            ideal_ms = (cell.fwd_bytes + cell.bwd_bytes) / world / (peak_now * 1e9) * 1e3
+            if f + b > 2.0 * ideal_ms:
+                slow.append({"S": cell.S, "D": cell.D, "ms": round(f + b, 4),
+                             "ms_at_peak": round(ideal_ms, 4)})
+        strong = {"scaling": "strong", "rows_per_gpu": strong_rows, "ms_per_step": s_ms,
+                  "value": len(cells) * ROWS / (s_ms * 1e-3), "unit": "tokens/s",
+                  "rank_kernel_ms": {"min": min(strong_rank_ms), "max": max(strong_rank_ms)},
+                  "collective_ms": max(gather_floats(s_tail, device, world)),
+                  "launch_bound_cells": slow,
+                  "note": "the same 18 x 16 384 positions split over the ranks; compare "
+                          "ms_per_step with the N = 1 line's"}
 
     # ---- end to end: pinned host buffers -> public API -> host results
-    e2e = (run_e2e(args, cells, device, distributed) if not args.skip_e2e
-           else {"ms_per_step": float("inf"), "h2d": 0, "d2h": 0, "steps": 0})
+    e2e = (run_e2e(args, cells, device, distributed, world) if not args.skip_e2e
+           else {"ms_per_step": float("inf"), "h2d": 0, "d2h": 0, "steps": 0, "pcie": None})
     if distributed:
+        import torch.distributed as dist
         worst = torch.tensor([e2e["ms_per_step"]], device=device, dtype=torch.float64)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
         e2e["ms_per_step"] = float(worst.item())
     e2e_value = tokens_per_step / (e2e["ms_per_step"] * 1e-3)
+    torch.cuda.synchronize()
+    gave_up = _native.error_flag()   # the sticky "a bounded wait ran out" flag of this device
 
     if rank != 0:
         return
@@ -364,7 +449,12 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     bwd_gbs = bwd_bytes / (sum(bwd_ms) * 1e-3) / 1e9
     fwd_gbs = fwd_bytes / (sum(fwd_ms) * 1e-3) / 1e9
     both_gbs = (bwd_bytes + fwd_bytes) / ((sum(bwd_ms) + sum(fwd_ms)) * 1e-3) / 1e9
-    ratio = traffic_ratio()
+    ratios = traffic_ratios()
+    # DRAM traffic of the average backward launch: every cell weighted by the ratio measured
+    # for the kernel family that serves it (None when a family has no capture on record).
+    traffic = None
+    if ratios and all(c.family in ratios for c in cells):
+        traffic = sum(ratios[c.family] * c.bwd_bytes for c in cells) / len(cells)
     per_cell = []
     for cell, f, b in zip(cells, fwd_ms, bwd_ms):
         per_cell.append({
@@ -374,16 +464,18 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "bwd_gbs": round(cell.bwd_bytes / (b * 1e-3) / 1e9, 1),
             "gbs": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9, 1),
             "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
-            "one_pass_backward": cell.saves_output,
+            "backward_kernel": cell.family,
         })
-    # The CPU oracle is timed at N = 1 only (under torchrun every rank is held to one thread).
+    # The CPU oracle is timed at N = 1 only (the reference arm reports it at every N).
     run_cpu = not args.skip_cpu and world == 1
+    if run_cpu:
+        use_all_host_threads()
     cpu_rate, cpu_seconds, threads = (cpu_oracle_tokens_per_s(CPU_SAMPLE_ROWS) if run_cpu
                                       else (None, 0.0, 0))
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong" if args.strong and world > 1 else "weak",
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None,
         "dtype": "bf16 storage / fp32 arithmetic", "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "cells": len(cells),
@@ -395,23 +487,68 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
         "roofline": {"bound": "hbm", "kernel": "backward (dominant: 2/3 of the bytes)",
                      "achieved": bwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": bwd_gbs / peak,
-                     "traffic": None if ratio is None else ratio * bwd_bytes / len(cells),
+                     "traffic": traffic,
+                     "traffic_over_algorithmic_by_kernel": ratios or None,
                      "algorithmic_bytes_per_launch": bwd_bytes / len(cells),
                      "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak}},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
                 "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e2e["ms_per_step"],
-                "steps": e2e["steps"]},
+                "steps": e2e["steps"], "pcie_measured_gbs": e2e["pcie"]},
         "cpu_baseline": ({"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                           "sample": f"PyTorch oracle port, all 18 cells at {CPU_SAMPLE_ROWS} rows "
                                     f"each ({cpu_seconds:.1f} s of CPU work)"} if run_cpu else None),
         "gpu_launches": args.steps * len(cells) * 3,
         "clocks": clocks.summary(),
+        "ranks": {"kernel_ms_per_step": {"min": min(rank_kernel_ms), "max": max(rank_kernel_ms)},
+                  "collective_ms_per_step": max(rank_tail_ms) if distributed else 0.0,
+                  "note": "kernel_ms: a rank's own forward+backward launches; collective_ms: the "
+                          "FP32 all-reduce of the 43 008 query-gradient floats plus the BF16 "
+                          "cast, including the wait for the slowest rank"},
+        "strong": strong,
+        "wait_gave_up_flag": gave_up,
         "cells": per_cell,
     }
     print(json.dumps(line), flush=True)
 
 
-def run_e2e(args, cells, device, distributed) -> dict:
+def pinned_copy_probe(device, distributed, world) -> dict:
+    """Plain pinned-memory copies, all ranks at once, both directions at once: the ceiling of
+    the end-to-end leg on this host.  256 MiB each way per repetition, three repetitions,
+    GB/s per direction: this rank's own figure is gathered so the line shows the slowest
+    rank, the fastest and the aggregate."""
+    import torch.distributed as dist
+    size = 256 * 1024 * 1024
+    host_in = torch.empty(size, dtype=torch.uint8).pin_memory()
+    host_out = torch.empty(size, dtype=torch.uint8).pin_memory()
+    dev_in = torch.empty(size, device=device, dtype=torch.uint8)
+    dev_out = torch.zeros(size, device=device, dtype=torch.uint8)
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def both_ways(repeats):
+        events = []
+        for stream, dst, src in ((up, dev_in, host_in), (down, host_out, dev_out)):
+            with torch.cuda.stream(stream):
+                first = stream.record_event(torch.cuda.Event(enable_timing=True))
+                for _ in range(repeats):
+                    dst.copy_(src, non_blocking=True)
+                last = stream.record_event(torch.cuda.Event(enable_timing=True))
+            events.append((first, last))
+        torch.cuda.synchronize()
+        return [repeats * size / (first.elapsed_time(last) * 1e-3) / 1e9 for first, last in events]
+
+    both_ways(1)
+    if distributed:
+        dist.barrier()
+    h2d, d2h = both_ways(3)
+    every_h2d = gather_floats(h2d, device, world)
+    every_d2h = gather_floats(d2h, device, world)
+    return {"ranks_copying_at_once": world, "duplex": True,
+            "h2d_per_rank": {"min": min(every_h2d), "max": max(every_h2d)},
+            "d2h_per_rank": {"min": min(every_d2h), "max": max(every_d2h)},
+            "h2d_aggregate": sum(every_h2d), "d2h_aggregate": sum(every_d2h)}
+
+
+def run_e2e(args, cells, device, distributed, world=1) -> dict:
     """The same sweep through `attnres()` + autograd with every input starting in pinned
     host memory and every result (out, value gradients, query gradient) copied back.
 
@@ -514,7 +651,11 @@ def run_e2e(args, cells, device, distributed) -> dict:
     if distributed:
         dist.barrier()
     torch.cuda.synchronize()
-    return {"ms_per_step": start.elapsed_time(stop) / steps, "h2d": h2d, "d2h": d2h, "steps": steps}
+    ms_per_step = start.elapsed_time(stop) / steps
+    pcie = pinned_copy_probe(device, distributed, world)
+    # the leg's own copy rate per direction and rank, next to what plain copies reach here
+    pcie["e2e_leg_per_rank_per_direction"] = h2d / (ms_per_step * 1e-3) / 1e9
+    return {"ms_per_step": ms_per_step, "h2d": h2d, "d2h": d2h, "steps": steps, "pcie": pcie}
 
 
 def run_single_cell(args) -> None:
@@ -632,7 +773,6 @@ def run_single_cell(args) -> None:
 
 
 def main() -> None:
-    global ROWS
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
@@ -652,8 +792,8 @@ def main() -> None:
     parser.add_argument("--two-pass", action="store_true",
                         help="--cell: never save the output residual (staged backward)")
     parser.add_argument("--strong", action="store_true",
-                        help="N > 1: split the 16 384 rows of every cell over the ranks (strong "
-                             "scaling) instead of giving every rank its own 16 384 (the default)")
+                        help="kept for old command lines: the strong-scaling record (the 16 384 "
+                             "rows of every cell split over the ranks) is part of every N > 1 line")
     args = parser.parse_args()
     if args.cell is not None:
         run_single_cell(args)
@@ -668,9 +808,6 @@ def main() -> None:
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU fallback")
-    if args.strong and world > 1:
-        # every rank takes an equal share of the rows (16 384 is a multiple of 2, 4 and 8)
-        ROWS = ROWS // world
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)

@@ -7,7 +7,9 @@ state of the CUDA library.  ``attnres.accumulate`` and ``attnres.parallel`` are 
 from . import api as _api
 from . import modules as _modules
 
-__version__ = "0.1.0"
+# The version of the reference API this package is a drop-in for (tests/test_info.py:16 of the
+# reference pins it).
+__version__ = "2.0.1"
 attnres = _api.attnres
 LearnedQuery = _modules.LearnedQuery
 

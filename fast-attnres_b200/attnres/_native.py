@@ -6,10 +6,10 @@ call raises.  Build it with ``python fast-attnres_b200/build.py``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int32, c_int64, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 FLAG_FORCE_GENERIC = 1
 FLAG_PREFER_STREAM = 2
 FLAG_ACCUMULATE_DV = 4
@@ -25,6 +25,7 @@ SIGNATURES = {
     "attnres_b200_kernel_family": (c_char_p, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "attnres_b200_dq_workspace_rows": (c_int32, [c_int64, c_int32, c_int32, c_int32, c_int32]),
     "attnres_b200_error_flag": (c_int32, [ctypes.POINTER(c_int32), c_int32]),
+    "attnres_b200_selftest_wait_limit": (c_int32, [c_void_p, c_uint64, c_void_p]),
     "attnres_b200_forward": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
         c_int32, c_int64, c_int32, c_int32,
@@ -157,6 +158,12 @@ def error_flag(clear: bool = False) -> int:
     value = c_int32(0)
     check(load().attnres_b200_error_flag(ctypes.byref(value), int(clear)), "attnres_b200_error_flag")
     return int(value.value)
+
+
+def selftest_wait_limit(scratch_ptr, limit_ns, stream) -> None:
+    """Run the library's bounded-wait self-test: afterwards ``error_flag()`` reads 1."""
+    check(load().attnres_b200_selftest_wait_limit(scratch_ptr, int(limit_ns), stream),
+          "attnres_b200_selftest_wait_limit")
 
 
 def kernel_family(S, D, R, aligned, backward_pass) -> str:

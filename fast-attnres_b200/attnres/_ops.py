@@ -46,11 +46,12 @@ def set_kernel_flags(flags: int) -> int:
 
 
 def _save_residual(count: int, width: int, rank: int) -> bool:
-    """Whether the forward also writes the BF16 residual of its output.
+    """Whether the forward also writes the 16-bit residual of its output.
 
-    The library's one-pass backward for long source lists needs the forward's result to
-    about 16 mantissa bits (output + residual); the decision depends on the shape only, so
-    the fake kernels below make the same one.
+    The library's one-pass backward for long source lists needs the forward's FP32 result
+    (the BF16 output plus the 16 bits its rounding dropped, an int16 tensor of the output's
+    shape); the decision depends on the shape only, so the fake kernels below make the same
+    one.
     """
     return bool(_flags & _native.FLAG_PREFER_STREAM) or \
         _native.wants_output_residual(int(count), int(width), int(rank))
@@ -69,6 +70,14 @@ def _require_cuda_bf16(tensors, query) -> None:
         raise TypeError("attnres_b200 operators require BF16 storage")
     if not query.is_cuda or any(not t.is_cuda for t in tensors):
         raise RuntimeError("attnres_b200 operators require CUDA tensors")
+
+
+def _require_saved_output(out, residual) -> None:
+    """`out` is the forward's BF16 output when its int16 residual was written, else both are
+    0-element stand-ins."""
+    if residual.numel() and (out.dtype != torch.bfloat16 or residual.dtype != torch.int16
+                             or out.shape != residual.shape):
+        raise TypeError("the saved output must be BF16 with an int16 residual of the same shape")
 
 
 def _source_table(sources):
@@ -106,7 +115,7 @@ def _run_forward(kept, ptrs, row_strides, feat_strides, shape, query, eps, scale
     if keep_residual is None:
         keep_residual = _save_residual(S, D, R)
     residual = torch.empty(tuple(shape) if keep_residual else (0,), device=device,
-                           dtype=torch.bfloat16)
+                           dtype=torch.int16)
     with torch.cuda.device(device):
         _native.forward(ptrs, row_strides, feat_strides, S, N, D, R,
                         query.data_ptr(), int(query.stride(0)), float(eps), float(scale),
@@ -165,7 +174,7 @@ def _(values, query, eps, scale):
     return (values.new_empty(values.shape[1:]),
             values.new_empty((values.shape[0], rows), dtype=torch.float32),
             values.new_empty((2, rows), dtype=torch.float32),
-            values.new_empty(values.shape[1:] if keep else (0,)))
+            values.new_empty(values.shape[1:] if keep else (0,), dtype=torch.int16))
 
 
 @_custom_op("attnres_b200::read_packed_backward", mutates_args=(), device_types="cuda")
@@ -173,7 +182,8 @@ def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output:
                          logits: torch.Tensor, stats: torch.Tensor, out: torch.Tensor,
                          residual: torch.Tensor, eps: float, scale: float,
                          need_values: bool, need_query: bool) -> tuple[torch.Tensor, torch.Tensor]:
-    _require_cuda_bf16((values, grad_output, out, residual), query)
+    _require_cuda_bf16((values, grad_output), query)
+    _require_saved_output(out, residual)
     kept, ptrs, row_strides, feat_strides = _packed_table(values)
     shape = values.shape[1:]
     count, rows, width = values.shape[0], _rows(shape), int(shape[-1])
@@ -245,7 +255,7 @@ def _(sources, query, eps, scale):
     return (first.new_empty(first.shape),
             first.new_empty((len(sources), rows), dtype=torch.float32),
             first.new_empty((2, rows), dtype=torch.float32),
-            first.new_empty(first.shape if keep else (0,)))
+            first.new_empty(first.shape if keep else (0,), dtype=torch.int16))
 
 
 @_custom_op("attnres_b200::read_sources_backward", mutates_args=(), device_types="cuda",
@@ -254,7 +264,8 @@ def read_sources_backward(sources: list[torch.Tensor], query: torch.Tensor,
                           grad_output: torch.Tensor, logits: torch.Tensor, stats: torch.Tensor,
                           out: torch.Tensor, residual: torch.Tensor,
                           eps: float, scale: float) -> list[torch.Tensor]:
-    _require_cuda_bf16((*sources, grad_output, out, residual), query)
+    _require_cuda_bf16((*sources, grad_output), query)
+    _require_saved_output(out, residual)
     kept, ptrs, row_strides, feat_strides = _source_table(sources)
     shape = sources[0].shape
     grads = [torch.empty(tuple(shape), device=query.device, dtype=torch.bfloat16)

@@ -31,7 +31,7 @@ from ._sources import DEFAULT_EPS, check_packed, check_sources
 def _check_buffers(buffers, shapes, device) -> None:
     if len(buffers) != len(shapes):
         raise ValueError("one gradient buffer per source is required")
-    seen = set()
+    spans = []
     for buffer, shape in zip(buffers, shapes):
         if not isinstance(buffer, torch.Tensor):
             raise TypeError("gradient buffers must be tensors")
@@ -45,11 +45,13 @@ def _check_buffers(buffers, shapes, device) -> None:
             raise ValueError("gradient buffers must be contiguous")
         if buffer.requires_grad:
             raise ValueError("gradient buffers must not require grad")
-        if buffer.data_ptr() in seen:
-            # the kernels prefetch a buffer row before they add to it: two sources sharing
-            # one buffer would lose an update
-            raise ValueError("every source needs its own gradient buffer")
-        seen.add(buffer.data_ptr())
+        spans.append((buffer.data_ptr(), buffer.data_ptr() + buffer.numel() * buffer.element_size()))
+    # The kernels fetch a buffer row before they add to it: two sources whose buffers share
+    # any memory (the same tensor, or overlapping views of one storage) would lose an update.
+    spans.sort()
+    for (_, end), (start, _) in zip(spans, spans[1:]):
+        if start < end:
+            raise ValueError("every source needs its own gradient buffer (buffers overlap)")
 
 
 class _AccumulatingRead(torch.autograd.Function):

@@ -156,6 +156,60 @@ bool wants_output_residual(int S, int D, int R) {
   return D <= 1024 && stash.ctas_per_sm <= 2;
 }
 
+// Everything about a backward call that can be judged without touching the device or the
+// dquery workspace; shared by both backward entry points so they refuse the same calls with
+// the same codes.
+int check_backward_args(const void* const* src_ptrs, const int64_t* src_row_stride,
+                        const int64_t* src_feat_stride, int32_t S, int64_t N, int32_t D, int32_t R,
+                        const void* query, float eps, float scale, const void* grad_out,
+                        const float* logits, const float* stats, void* const* dsrc_ptrs,
+                        const int64_t* dsrc_row_stride, const void* dq_bf16, const float* dq_f32,
+                        uint32_t flags) {
+  if (int st = check_shape(S, N, D, R)) return st;
+  if (int st = check_scalars(eps, scale)) return st;
+  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM |
+                ATTNRES_B200_FLAG_ACCUMULATE_DV))
+    return ATTNRES_B200_ERR_BAD_FLAGS;
+  if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !grad_out || !logits || !stats)
+    return ATTNRES_B200_ERR_NULL_POINTER;
+  const bool accumulate = (flags & ATTNRES_B200_FLAG_ACCUMULATE_DV) != 0;
+  if (accumulate && dsrc_ptrs == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  const bool want_dq = dq_bf16 != nullptr || dq_f32 != nullptr;
+  const bool want_dv = dsrc_ptrs != nullptr;
+  if (!want_dq && !want_dv) return ATTNRES_B200_ERR_NOTHING_TO_DO;
+  if (want_dv && dsrc_row_stride == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  if (!aligned2(query) || !aligned2(grad_out) || (dq_bf16 && !aligned2(dq_bf16)))
+    return ATTNRES_B200_ERR_MISALIGNED;
+  for (int s = 0; s < S; ++s) {
+    if (src_ptrs[s] == nullptr || (want_dv && dsrc_ptrs[s] == nullptr))
+      return ATTNRES_B200_ERR_NULL_POINTER;
+    if (!aligned2(src_ptrs[s]) || (want_dv && !aligned2(dsrc_ptrs[s])))
+      return ATTNRES_B200_ERR_MISALIGNED;
+  }
+  return ATTNRES_B200_OK;
+}
+
+// One CTA of one warp: lane 0 announces 32 bytes on a barrier, copies 16 and waits with the
+// kernels' bounded wait.  Exercises the give-up path without a fault or a hang.
+__global__ void selftest_wait_limit_kernel(const void* scratch16, uint64_t limit_ns) {
+  __shared__ __align__(16) unsigned char landing[32];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(&bar, 32u);
+    bulk_load(landing, scratch16, 16u, &bar);
+    mbar_wait(&bar, 0u, &abort_flag, limit_ns);
+    // The 16 bytes that were requested have landed long before the limit; hold the CTA a
+    // little all the same, as the kernels do after a wait that ran out.
+    const uint64_t start = global_timer_ns();
+    while (global_timer_ns() - start < 20000ull) {
+    }
+  }
+}
+
 }  // namespace
 }  // namespace attnres_b200
 
@@ -188,7 +242,13 @@ extern "C" const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t 
                                                   int32_t aligned, int32_t backward) {
   if (check_shape(S, 1, D, R) != ATTNRES_B200_OK) return "invalid";
   if (!aligned) return "generic";
-  if (backward) return (bwd_ring_supported(S, D, R) || tma_bwd_supported(S, D, R)) ? "tma" : "generic";
+  if (backward) {
+    // The one-pass kernel counts where the library's own policy asks the forward to save
+    // its output (long lists that no staged kernel takes, e.g. S = 129 at D = 8192).
+    const bool fast = bwd_ring_supported(S, D, R) || tma_bwd_supported(S, D, R) ||
+                      (bwd_stream_supported(S, D, R) && wants_output_residual(S, D, R));
+    return fast ? "tma" : "generic";
+  }
   return tma_fwd_supported(S, D, R) ? "tma" : "generic";
 }
 
@@ -284,22 +344,14 @@ extern "C" int attnres_b200_backward(
     float* dq_partials, int32_t dq_partial_rows,
     void* dq_bf16, float* dq_f32,
     uint32_t flags, void* stream) {
-  if (int st = check_shape(S, N, D, R)) return st;
-  if (int st = check_scalars(eps, scale)) return st;
-  if (flags & ~(ATTNRES_B200_FLAG_FORCE_GENERIC | ATTNRES_B200_FLAG_PREFER_STREAM |
-                ATTNRES_B200_FLAG_ACCUMULATE_DV))
-    return ATTNRES_B200_ERR_BAD_FLAGS;
-  if (!src_ptrs || !src_row_stride || !src_feat_stride || !query || !grad_out || !logits || !stats)
-    return ATTNRES_B200_ERR_NULL_POINTER;
+  if (int st = check_backward_args(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query, eps,
+                                   scale, grad_out, logits, stats, dsrc_ptrs, dsrc_row_stride,
+                                   dq_bf16, dq_f32, flags))
+    return st;
   const bool accumulate = (flags & ATTNRES_B200_FLAG_ACCUMULATE_DV) != 0;
-  if (accumulate && dsrc_ptrs == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
   const bool want_dq = dq_bf16 != nullptr || dq_f32 != nullptr;
   const bool want_dv = dsrc_ptrs != nullptr;
-  if (!want_dq && !want_dv) return ATTNRES_B200_ERR_NOTHING_TO_DO;
-  if (want_dv && dsrc_row_stride == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
   if (want_dq && dq_partials == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
-  if (!aligned2(query) || !aligned2(grad_out) || (dq_bf16 && !aligned2(dq_bf16)))
-    return ATTNRES_B200_ERR_MISALIGNED;
 
   BwdParams p;
   bool vec = false;
@@ -386,7 +438,6 @@ namespace {
 // not a device address; static_scratch_address() below asks the runtime for the address.
 static __device__ __align__(256) float g_static_dq_scratch[ATTNRES_B200_STATIC_SCRATCH_FLOATS];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 float* g_static_scratch_address[kMaxDevices] = {};
 
@@ -420,7 +471,15 @@ extern "C" int attnres_b200_backward_static_scratch(
     void* const* dsrc_ptrs, const int64_t* dsrc_row_stride,
     void* dq_bf16, float* dq_f32,
     uint32_t flags, void* stream) {
-  if (int st = check_shape(S, N, D, R)) return st;
+  if (int st = check_backward_args(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query, eps,
+                                   scale, grad_out, logits, stats, dsrc_ptrs, dsrc_row_stride,
+                                   dq_bf16, dq_f32, flags))
+    return st;
+  if (dq_bf16 == nullptr && dq_f32 == nullptr)  // value gradients only: no scratch involved
+    return attnres_b200_backward(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query,
+                                 query_stride, eps, scale, grad_out, go_row_stride, go_feat_stride,
+                                 logits, stats, out_saved, out_residual, dsrc_ptrs, dsrc_row_stride,
+                                 nullptr, 0, nullptr, nullptr, flags, stream);
   int device = 0;
   if (int st = current_device(&device)) return st;
   const int32_t rows = attnres_b200_dq_workspace_rows(N, S, D, R, device);
@@ -436,4 +495,13 @@ extern "C" int attnres_b200_backward_static_scratch(
                                logits, stats, out_saved, out_residual, dsrc_ptrs, dsrc_row_stride,
                                scratch, rows, dq_bf16,
                                dq_f32, flags, stream);
+}
+
+extern "C" int attnres_b200_selftest_wait_limit(const void* scratch16, uint64_t limit_ns,
+                                                void* stream) {
+  if (scratch16 == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  if (!aligned16(scratch16)) return ATTNRES_B200_ERR_MISALIGNED;
+  if (limit_ns < 1000ull || limit_ns > 100000000ull) return ATTNRES_B200_ERR_BAD_SCALAR;
+  selftest_wait_limit_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(scratch16, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
 }

@@ -403,7 +403,8 @@ template <int G, int SE, bool FULL, int TAIL0>
 inline int launch_bwd_ring_instance(const BwdParams& p, const BwdRingPlan& plan, int grid,
                                     cudaStream_t stream) {
   auto kernel = bwd_ring_kernel<G, SE, FULL, TAIL0>;
-  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  static SmemGrant grant;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes, grant)) return st;
   kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }

@@ -200,6 +200,15 @@ __device__ __forceinline__ void cluster_sync_all() {
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Last statement of every thread of a clustered launch: no CTA retires (and hands its shared
+// memory to another CTA) while a peer may still store into it or arrive on its barriers.
+// Not `.aligned`: of the producer warp only lane 0 is still running when it gets here.
+// Every wait before it is bounded, so every thread gets here.
+__device__ __forceinline__ void cluster_exit_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n"
+               "barrier.cluster.wait.acquire;" ::: "memory");
+}
+
 // Address of the same shared-memory location in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
@@ -334,6 +343,8 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
         while (global_timer_ns() - start < 200000ull) {
         }
       }
+      // The warp's other lanes have exited (exited threads do not count at the barrier).
+      if (C > 1) cluster_exit_sync();
     }
     return;
   }
@@ -552,12 +563,15 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
       }
     }
   }
+  if (C > 1) cluster_exit_sync();
 }
 
 template <int NV, int CL, bool GROUPS, int MAXT, bool FULL>
 inline int launch_bwd_stash(const BwdParams& p, const BwdPlan& plan, int grid, int threads,
                             cudaStream_t stream) {
-  if (int st = prepare_kernel(bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL>, plan.smem_bytes)) return st;
+  static SmemGrant grant;
+  if (int st = prepare_kernel(bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL>, plan.smem_bytes, grant))
+    return st;
   if (plan.cluster == 1) {
     bwd_tma_kernel<NV, CL, GROUPS, MAXT, FULL><<<grid, threads, plan.smem_bytes, stream>>>(p, plan);
   } else {

@@ -3,9 +3,10 @@
 //
 // The staged ("stash") backward needs all S rows of a position in shared memory because
 // delta = sum_s p_s (v_s . dO) is only known after every source has been reduced.  When the
-// forward also saved its result (the BF16 output and the BF16 residual its rounding dropped),
-// delta = sum_d dO_d * (out_d + residual_d) is available BEFORE any source is read, and every
-// source can be finished the moment it arrives:
+// forward also saved its result (the BF16 output and the 16 bits of the FP32 result that its
+// rounding dropped, see split_low16x2), delta = sum_d dO_d * result_d is available in full
+// FP32 precision BEFORE any source is read, and every source can be finished the moment it
+// arrives:
 //
 //   per position   the group (G warps, four 16-byte chunks per lane, as in the forward ring
 //                  kernel) loads dO, out and residual from its ring, keeps dO in registers
@@ -17,7 +18,7 @@
 //
 // Shared memory holds only the ring, so any S fits, three CTAs stay resident per SM and the
 // loads of later sources overlap the stores of earlier ones.  The price is 6*D extra bytes per
-// position (one more BF16 row written by the forward, two more read here); which shapes take
+// position (one more 16-bit row written by the forward, two more read here); which shapes take
 // this kernel is decided by attnres_b200_wants_output_residual from measurements.
 //
 // In accumulate mode (template parameter ACC) the existing gradient row of every source rides
@@ -248,7 +249,7 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
 
-    // ---- dO into registers; delta = sum_d dO * (out + residual)
+    // ---- dO into registers; delta = sum_d dO * (the forward's FP32 result)
     float2 g2[NV][4];
     float delta;
     {
@@ -267,14 +268,11 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
       for (int j = 0; j < NV; ++j) {
         if (row_ok(j)) {
           unpack_pairs(gp[j * L], g2[j]);
-          float2 o[4], r[4];
-          unpack_pairs(op[j * L], o);
-          unpack_pairs(rp[j * L], r);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            acc = __ffma2_rn(g2[j][k], o[k], acc);
-            acc = __ffma2_rn(g2[j][k], r[k], acc);
-          }
+          const uint4 o = op[j * L], r = rp[j * L];
+          acc = __ffma2_rn(g2[j][0], join_low16x2(o.x, r.x), acc);
+          acc = __ffma2_rn(g2[j][1], join_low16x2(o.y, r.y), acc);
+          acc = __ffma2_rn(g2[j][2], join_low16x2(o.z, r.z), acc);
+          acc = __ffma2_rn(g2[j][3], join_low16x2(o.w, r.w), acc);
         } else {
 #pragma unroll
           for (int k = 0; k < 4; ++k) g2[j][k] = make_float2(0.f, 0.f);
@@ -468,7 +466,8 @@ template <int G, bool FULL, int TAIL0, bool SR, bool ZE, bool ACC>
 inline int launch_bwd_stream_variant(const BwdParams& p, const BwdStreamPlan& plan, int grid,
                                      cudaStream_t stream) {
   auto kernel = bwd_stream_kernel<G, FULL, TAIL0, SR, ZE, ACC>;
-  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  static SmemGrant grant;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes, grant)) return st;
   kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }

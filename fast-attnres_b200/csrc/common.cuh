@@ -42,8 +42,8 @@ struct FwdParams {
   float scale;
   __nv_bfloat16* out;
   int64_t out_row_stride;
-  // Optional BF16 [N,D] (contiguous): the part of the FP32 result that the BF16 rounding of
-  // `out` dropped, so out + residual carries about 16 mantissa bits.  NULL skips it.
+  // Optional 16-bit [N,D] (contiguous): the part of the FP32 result that the BF16 rounding of
+  // `out` dropped (split_low16x2 below), so out + residual is the FP32 result.  NULL skips it.
   __nv_bfloat16* out_residual;
   float* logits;  // [S,N]
   float* stats;   // [2,N]: max, 1/denominator
@@ -67,9 +67,9 @@ struct BwdParams {
   int64_t go_feat_stride;
   const float* logits;
   const float* stats;
-  // Optional: the forward's BF16 output and its residual (both [N,D] contiguous).  With them
-  // delta = sum_d dO * (out + residual) is known before any source is read, which lets the
-  // streaming backward finish every source in one pass.
+  // Optional: the forward's BF16 output and its 16-bit residual (both [N,D] contiguous),
+  // together the forward's FP32 result.  With them delta = sum_d dO * result is known before
+  // any source is read, which lets the streaming backward finish every source in one pass.
   const __nv_bfloat16* out_saved;
   const __nv_bfloat16* out_residual;
   float* dq_partials;  // [gridDim.x, R]
@@ -86,6 +86,37 @@ __device__ __forceinline__ float bf16x2_hi(uint32_t w) { return __uint_as_float(
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// The saved output.  The forward rounds its FP32 result to BF16 (`out`) and, when asked, also
+// keeps what the rounding dropped, as one signed 16-bit integer per element:
+//     low = float_bits(result) - (bf16_bits(out) << 16)            (in -32768 .. 32768)
+// Round-to-nearest moves the upper half of the FP32 pattern by at most one step, so the
+// difference fits 16 bits except for the tie that rounds DOWN to even (+32768), which is
+// stored as 32767 (one FP32 ulp off, one element in 2^17).  The backward gets the FP32
+// result back with an integer add, so `out` + `low` is a full FP32 copy of the output in the
+// space of two BF16 rows.  (The reference saves a separate FP32 copy,
+// src/attnres/_kernels/fixed_tail.py:917-919.)
+//
+// Packed form: `hi` holds two BF16 outputs, the returned word their two 16-bit remainders.
+__device__ __forceinline__ uint32_t split_low16x2(float x0, float x1, uint32_t hi) {
+  int d0 = (int)(__float_as_uint(x0) - (hi << 16));
+  int d1 = (int)(__float_as_uint(x1) - (hi & 0xffff0000u));
+  d0 = min(d0, 32767);
+  d1 = min(d1, 32767);
+  return __byte_perm((uint32_t)d0, (uint32_t)d1, 0x5410);
+}
+
+__device__ __forceinline__ unsigned short split_low16(float x, unsigned short hi) {
+  int d = (int)(__float_as_uint(x) - ((uint32_t)hi << 16));
+  return (unsigned short)min(d, 32767);
+}
+
+// Inverse of split_low16x2: the two FP32 results from the packed BF16 pair and remainders.
+__device__ __forceinline__ float2 join_low16x2(uint32_t hi, uint32_t low) {
+  const uint32_t x0 = (hi << 16) + (uint32_t)(int)(short)(low & 0xffffu);
+  const uint32_t x1 = (hi & 0xffff0000u) + (uint32_t)((int)low >> 16);
+  return make_float2(__uint_as_float(x0), __uint_as_float(x1));
 }
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {

@@ -370,8 +370,7 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
         for (int k = 0; k < 4; ++k) {
           const float2 o = __fmul2_rn(acc[j][k], i2);
           hi[k] = pack_bf16x2(o.x, o.y);
-          // what the BF16 rounding dropped, itself rounded to BF16
-          lo[k] = pack_bf16x2(o.x - bf16x2_lo(hi[k]), o.y - bf16x2_hi(hi[k]));
+          lo[k] = split_low16x2(o.x, o.y, hi[k]);  // what the BF16 rounding dropped
         }
         *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         if (rrow != nullptr)
@@ -395,7 +394,8 @@ template <int G, int TAIL0>
 inline int launch_fwd_ring(const FwdParams& p, const FwdRingPlan& plan, int grid,
                            cudaStream_t stream) {
   auto kernel = fwd_ring_kernel<G, TAIL0, (G == 8 && TAIL0 >= 0)>;
-  if (int st = prepare_kernel(kernel, plan.smem_bytes)) return st;
+  static SmemGrant grant;
+  if (int st = prepare_kernel(kernel, plan.smem_bytes, grant)) return st;
   kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }

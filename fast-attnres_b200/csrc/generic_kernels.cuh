@@ -164,7 +164,8 @@ fwd_generic_kernel(const __grid_constant__ FwdParams p) {
           const float o = acc[j * VEC + e] / run_sum;
           const __nv_bfloat16 hi = __float2bfloat16_rn(o);
           orow[d] = hi;
-          if (rrow != nullptr) rrow[d] = __float2bfloat16_rn(o - __bfloat162float(hi));
+          if (rrow != nullptr)
+            reinterpret_cast<unsigned short*>(rrow)[d] = split_low16(o, __bfloat16_as_ushort(hi));
         }
       }
     }
@@ -341,21 +342,24 @@ bwd_generic_kernel(const __grid_constant__ BwdParams p) {
 __global__ void __launch_bounds__(256)
 dq_reduce_kernel(const float* __restrict__ partials, int rows, int R,
                  __nv_bfloat16* __restrict__ dq_bf16, float* __restrict__ dq_f32) {
-  __shared__ float sm[8][33];
+  __shared__ double sm[8][33];
   const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
   const int r = blockIdx.x * 32 + col;
-  float sum = 0.f;
+  // The partial rows are summed in FP64, so this stage adds no rounding of its own: the
+  // result is the FP32 rounding of the exact sum of the partials.
+  double sum = 0.0;
   if (r < R) {
-    for (int row = grp; row < rows; row += 8) sum += partials[(int64_t)row * R + r];
+    for (int row = grp; row < rows; row += 8) sum += (double)partials[(int64_t)row * R + r];
   }
   sm[grp][col] = sum;
   __syncthreads();
   if (grp == 0 && r < R) {
-    float total = 0.f;
+    double total = 0.0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) total += sm[k][col];
-    if (dq_f32 != nullptr) dq_f32[r] = total;
-    if (dq_bf16 != nullptr) dq_bf16[r] = __float2bfloat16_rn(total);
+    const float rounded = (float)total;
+    if (dq_f32 != nullptr) dq_f32[r] = rounded;
+    if (dq_bf16 != nullptr) dq_bf16[r] = __float2bfloat16_rn(rounded);
   }
 }
 

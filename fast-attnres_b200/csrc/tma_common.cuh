@@ -4,8 +4,12 @@
 // Every wait on an mbarrier is bounded: after about two seconds the CTA sets an
 // abort flag, stops waiting (later waits return at once), finishes its barrier
 // sequence with meaningless data and raises the device error flag the host can
-// read with attnres_b200_error_flag().
+// read with attnres_b200_error_flag().  The launch itself still returns "ok" (it
+// is asynchronous): callers poll the flag at step boundaries.  CTAs of a cluster
+// additionally meet at a cluster barrier before they retire.
 #pragma once
+
+#include <atomic>
 
 #include "common.cuh"
 
@@ -59,8 +63,10 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // Bounded wait.  Returns false (and latches the CTA abort flag) on timeout or
-// when another thread of the CTA has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// when another thread of the CTA has already given up.  The kernels wait with the
+// default limit; the library's self-test passes a short one to run the give-up path.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitTimeoutNs) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const uint64_t start = global_timer_ns();
@@ -68,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - start > kWaitTimeoutNs) {
+      if (global_timer_ns() - start > limit_ns) {
         *abort_flag = 1;
         atomicOr(&g_error_flag, 1);
         return false;
@@ -110,12 +116,35 @@ inline bool tma_shape_ok(int D, int R) {
   return D >= kTmaMinWidth && D % 8 == 0 && (D - R) % 8 == 0;
 }
 
+// Largest dynamic shared-memory size already granted to one kernel instance, per device.
+// Every launch function owns a static one, so the attribute is set once per (instance,
+// device, size) instead of on every launch.  (cudaDeviceReset discards the attribute
+// together with the context; a process that resets a device must reload the library.)
+constexpr int kMaxDevices = 64;
+struct SmemGrant {
+  std::atomic<uint32_t> bytes[kMaxDevices];
+};
+
 template <typename Kernel>
-inline int prepare_kernel(Kernel kernel, uint32_t smem_bytes) {
+inline int prepare_kernel(Kernel kernel, uint32_t smem_bytes, SmemGrant& grant) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return 9;
+  }
+  const bool cached = device >= 0 && device < kMaxDevices;
+  if (cached && grant.bytes[device].load(std::memory_order_acquire) >= smem_bytes) return 0;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) !=
       cudaSuccess) {
     cudaGetLastError();
     return 9;
+  }
+  if (cached) {
+    // Monotonic: a concurrent caller that raised the limit further keeps its value.
+    uint32_t seen = grant.bytes[device].load(std::memory_order_relaxed);
+    while (seen < smem_bytes &&
+           !grant.bytes[device].compare_exchange_weak(seen, smem_bytes, std::memory_order_release)) {
+    }
   }
   return 0;
 }

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define ATTNRES_B200_ABI_VERSION 2
+#define ATTNRES_B200_ABI_VERSION 3
 /* Envelope of the reference operator (src/attnres/_sources.py:12-13). */
 #define ATTNRES_B200_MAX_SOURCES 129
 #define ATTNRES_B200_MAX_WIDTH 8192
@@ -99,11 +99,16 @@ const char* attnres_b200_status_string(int status);
  *                      [S,N,D] tensor is passed as base + s*stride(0))
  *   query              device BF16 [R], element stride `query_stride`
  *   out                device BF16 [N,D], row stride `out_row_stride`, feature stride 1
- *   out_residual       optional device BF16 [N,D] contiguous: what the BF16 rounding of `out`
- *                      dropped (out + out_residual carries about 16 mantissa bits of the FP32
- *                      result).  Ask attnres_b200_wants_output_residual whether the backward
- *                      of this shape profits from it; NULL skips it.  The reference saves a
- *                      full FP32 copy of the output instead (fixed_tail.py:917-919).
+ *   out_residual       optional device int16 [N,D] contiguous: what the BF16 rounding of `out`
+ *                      dropped, so that the pair is a full FP32 copy of the result in the
+ *                      space of two BF16 rows:
+ *                        float_bits(result) = (bf16_bits(out) << 16) + out_residual
+ *                      (signed add; exact except for the one-in-2^17 tie that rounds down,
+ *                      which is one FP32 ulp off).  Ask attnres_b200_wants_output_residual
+ *                      whether the backward of this shape profits from it; NULL skips it.
+ *                      The reference saves a separate FP32 copy of the output
+ *                      (fixed_tail.py:917-919); its backward and this one then form
+ *                      delta = sum_d dO * result from the same FP32 values.
  *   logits             device FP32 [S,N] contiguous: scaled logits z_s
  *   stats              device FP32 [2,N] contiguous: row max, then 1/sum(exp(z-max))
  *   stream             a cudaStream_t (0 = legacy default stream)
@@ -144,7 +149,7 @@ int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t 
  *
  *   grad_out           device BF16 [N,D] with arbitrary row/feature strides
  *   logits, stats      as written by attnres_b200_forward for the same inputs
- *   out_saved,         optional: `out` and `out_residual` of the forward (BF16 [N,D]
+ *   out_saved,         optional: `out` and `out_residual` of the forward (16-bit [N,D]
  *   out_residual       contiguous).  Both or neither; NULL for both is always correct.
  *   dsrc_ptrs[s]       device BF16 [N,D] gradient of source s, row stride
  *                      dsrc_row_stride[s], feature stride 1 (host arrays, length S).
@@ -158,7 +163,7 @@ int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t 
  *                      BF16 cast.  Both NULL skips the query gradient.
  *
  * The query gradient is reduced in a fixed order, so repeated calls are
- * bit-identical.
+ * bit-identical; the second stage adds the partial rows in FP64 and rounds once.
  */
 int attnres_b200_backward(
     const void* const* src_ptrs, const int64_t* src_row_stride,
@@ -178,7 +183,9 @@ int attnres_b200_backward(
  * Name of the kernel family the library would pick for a call of this shape
  * ("tma" or "generic"), for logs and tests.  `aligned` is nonzero when every
  * pointer is 16-byte aligned, every row stride a multiple of 8 elements and
- * every feature stride 1.  `backward` selects the backward policy.
+ * every feature stride 1.  `backward` selects the backward policy, for a caller
+ * that follows attnres_b200_wants_output_residual (a backward that is handed no
+ * saved output although the shape wants one may fall back to "generic").
  */
 const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t aligned,
                                        int32_t backward);
@@ -204,9 +211,13 @@ const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t 
  *     exceed ATTNRES_B200_STATIC_SCRATCH_FLOATS (any N up to R = 2048; larger R
  *     only with few rows).  Otherwise nothing is launched and the call returns
  *     ATTNRES_B200_ERR_STATIC_SCRATCH; use attnres_b200_backward instead.
- *   - The first call on each device looks up the device address of the array
- *     (one driver query, cached per device).  Make that first call outside any
- *     CUDA stream capture.
+ *   - The first call on each device that asks for a query gradient looks up
+ *     the device address of the array (one driver query, cached per device for
+ *     the life of the process; a process that calls cudaDeviceReset must reload
+ *     the library).  Make that first call outside any CUDA stream capture.
+ *   - Arguments are checked exactly as attnres_b200_backward checks them, before
+ *     the size limit is looked at; a call with both `dq_*` NULL needs no scratch
+ *     and is never refused for its size.
  *   - All calls on a device share the one array.  Its contents are whatever the
  *     previous call left; this is harmless because every element the second
  *     stage reads is written by the first stage of the same call, so nothing has
@@ -233,9 +244,23 @@ int attnres_b200_backward_static_scratch(
  * device-side flag and finishes with meaningless results instead of hanging.
  * This call copies the flag of the current device to `*flag` (0 = no kernel ever
  * gave up) and optionally clears it.  It SYNCHRONISES the device: use it in
- * tests and after failures, not on the hot path.
+ * tests and after failures, not on the hot path.  A launch whose kernel gives
+ * up has long returned ATTNRES_B200_OK (launches are asynchronous), so a
+ * training loop should read the flag at step boundaries or before it trusts a
+ * checkpoint.
  */
 int attnres_b200_error_flag(int32_t* flag, int32_t clear);
+
+/*
+ * Self-test of the give-up path (no counterpart in the reference).  Launches one
+ * tiny CTA on `stream` that announces 32 bytes on a shared-memory barrier, copies
+ * only 16, and waits on it with the kernels' own bounded wait and a limit of
+ * `limit_ns` nanoseconds (1 000 .. 100 000 000).  The wait runs out, the CTA
+ * raises the device error flag and returns; nothing hangs and no memory outside
+ * the CTA is written.  `scratch16` is any 16-byte aligned device buffer of at
+ * least 16 readable bytes.  Afterwards attnres_b200_error_flag reports 1.
+ */
+int attnres_b200_selftest_wait_limit(const void* scratch16, uint64_t limit_ns, void* stream);
 
 #ifdef __cplusplus
 }

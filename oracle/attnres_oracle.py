@@ -99,6 +99,36 @@ def closed_form(values: np.ndarray, query: np.ndarray, upstream: np.ndarray | No
     return out, dv, dq
 
 
+def closed_form_dquery(values: torch.Tensor, query: torch.Tensor, upstream: torch.Tensor, *,
+                       eps: float = 2**-23, scale: float = 1.0, block_rows: int = 256
+                       ) -> torch.Tensor:
+    """Float64 query gradient of ``closed_form`` for ``[S, N, D]`` tensors on any device,
+    accumulated over blocks of rows so that large shapes need little memory.  The yardstick
+    for an FP32 query gradient: FP32 results differ from it by accumulated rounding only."""
+    rank = query.numel()
+    q = query.double()
+    total = torch.zeros(rank, dtype=torch.float64, device=values.device)
+    for first in range(0, values.shape[1], block_rows):
+        v = values[:, first:first + block_rows].double()
+        g = upstream[first:first + block_rows].double()
+        tail = v[..., -rank:]
+        r = torch.rsqrt(tail.square().mean(-1) + eps)            # [S, n]
+        k = tail * r[..., None]
+        z = scale * (k * q).sum(-1)
+        p = torch.softmax(z, 0)
+        dw = (v * g[None]).sum(-1)
+        dz = p * (dw - (p * dw).sum(0, keepdim=True))
+        total += scale * torch.einsum("sn,snr->r", dz, k)
+    return total
+
+
+def join_saved_output(out: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """The FP32 result the forward kernels computed, from the BF16 output and the int16
+    residual they save with it: float_bits = (bf16_bits(out) << 16) + residual."""
+    high = out.contiguous().view(torch.int16).to(torch.int32) << 16
+    return (high + residual.to(torch.int32)).view(torch.float32)
+
+
 def bf16_bits(tensor: torch.Tensor) -> np.ndarray:
     """The raw 16-bit patterns of a BF16 tensor as a uint16 array."""
     return tensor.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16).copy()

@@ -194,3 +194,38 @@ def test_accumulate_argument_checks():
                        good[0].device)
     with pytest.raises(ValueError, match="own gradient buffer"):
         _check_buffers([good[0], good[0], good[1]], shapes, good[0].device)
+    # overlapping views of one storage: each is contiguous with the right shape, but rows 2..3
+    # of the first are rows 0..1 of the second
+    storage = torch.zeros(6 * 16 + 4 * 16, dtype=torch.bfloat16)
+    first, second = storage[:64].view(4, 16), storage[32:96].view(4, 16)
+    with pytest.raises(ValueError, match="overlap"):
+        _check_buffers([first, second, good[2]], shapes, good[0].device)
+    # adjacent views of one storage do not overlap
+    _check_buffers([storage[:64].view(4, 16), storage[64:128].view(4, 16), good[2]], shapes,
+                   good[0].device)
+
+
+def test_info_command_keeps_the_reference_keys_and_runs_without_a_gpu():
+    """`python -m attnres.info [--json]` (tests/test_info.py:44-90 of the reference)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    import attnres
+    package_dir = Path(attnres.__file__).resolve().parents[1]
+    for flags in ([], ["--json"]):
+        done = subprocess.run([sys.executable, "-m", "attnres.info", *flags], cwd=package_dir,
+                              capture_output=True, text=True, timeout=300)
+        assert done.returncode == 0, done.stdout + done.stderr
+        if flags:
+            info = json.loads(done.stdout)
+            assert info["package"] == "fast-attnres"
+            assert info["version"] == attnres.__version__ == "2.0.1"
+            assert info["torch"] == torch.__version__
+            assert isinstance(info["cuda_available"], bool)
+            assert isinstance(info["triton_available"], bool)
+            assert info["library_present"] is True and info["library_abi"] == 3
+        else:
+            for text in ("fast-attnres 2.0.1", "torch:", "cuda available:", "triton available:",
+                         "attnres API: CUDA BF16 only", "library state: ABI 3"):
+                assert text in done.stdout

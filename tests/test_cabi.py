@@ -85,6 +85,37 @@ def test_backward_argument_errors_are_found_before_any_launch():
     assert call(dq=0x8001) == 7
 
 
+def test_static_scratch_backward_checks_arguments_like_the_workspace_backward():
+    """Same codes in the same order, found before the size limit or the device is looked at."""
+    lib = _native.load()
+    S, N, D, R = 2, 4, 16, 8
+    ptrs = _native.pointer_array([0x1000] * S)
+    strides = _native.int64_array([D] * S)
+    ones = _native.int64_array([1] * S)
+
+    def call(S=S, go=0x6000, dsrc=ptrs, dstr=strides, dq=0x8000, eps=2**-23, flags=0, R=R):
+        return lib.attnres_b200_backward_static_scratch(
+            ptrs, strides, ones, S, N, D, R, 0x2000, 1, eps, 1.0, go, D, 1, 0x4000, 0x5000,
+            None, None, dsrc, dstr, dq, None, flags, None)
+
+    assert call(S=0) == 2
+    assert call(R=17) == 4
+    assert call(eps=-1.0) == 6
+    assert call(flags=64) == 10
+    assert call(go=None) == 1
+    assert call(dsrc=None, dstr=None, dq=None) == 11
+    assert call(dstr=None) == 1
+    assert call(dq=0x8001) == 7
+
+
+def test_selftest_entry_point_checks_its_arguments():
+    lib = _native.load()
+    assert lib.attnres_b200_selftest_wait_limit(None, 1000000, None) == 1
+    assert lib.attnres_b200_selftest_wait_limit(0x1008, 1000000, None) == 7
+    assert lib.attnres_b200_selftest_wait_limit(0x1000, 10, None) == 6
+    assert lib.attnres_b200_selftest_wait_limit(0x1000, 10**12, None) == 6
+
+
 def test_output_residual_policy_is_a_pure_host_decision():
     # lists of up to four sources never want it; a position that fills an SM's shared
     # memory does, and so do full-width rows of 2048 and more with a full-rank query
@@ -119,7 +150,10 @@ def test_kernel_family_selection_is_a_pure_host_decision():
     assert _native.kernel_family(9, 2048, 2048, False, True) == "generic"
     assert _native.kernel_family(9, 3000, 127, True, False) == "generic"
     assert _native.kernel_family(49, 4096, 4096, True, True) == "tma"       # a 2-CTA cluster shares the row
-    assert _native.kernel_family(129, 8192, 8192, True, True) == "generic"  # 2.1 MB row: beyond 8 CTAs
+    # 2.1 MB per position: no staged kernel takes it, the one-pass kernel (whose forward saves
+    # the output) does
+    assert _native.kernel_family(129, 8192, 8192, True, True) == "tma"
+    assert _native.wants_output_residual(129, 8192, 8192)
     assert _native.kernel_family(49, 4096, 4096, True, False) == "tma"
     assert _native.kernel_family(2, 1024, 1024, False, False) == "generic"
     assert _native.kernel_family(0, 1024, 1024, True, False) == "invalid"

@@ -1,0 +1,108 @@
+"""Accuracy of the query gradient, and parity with the reference's Triton kernels.
+
+The query gradient is an FP32 sum over N*S terms that is rounded to BF16 once.  Comparing
+BF16 results only shows which elements happened to round to a neighbouring value; the first
+test therefore takes the FP32 form from the C ABI and measures its distance from the float64
+closed form, for the kernel that forms delta from the forward's saved FP32 result (one pass)
+and for the kernels that rebuild delta = sum_s p_s dw_s themselves (two passes).  The second
+test runs the reference's Triton kernels on the same GPU (when the reference is installed
+under baseline/_ref) and holds this library to their error, per shape.
+"""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import attnres_oracle as ao
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+BF16 = torch.bfloat16
+SWEEP = [(s, d, d) for d in (1024, 2048, 4096) for s in (2, 5, 9, 17, 25, 49)] + [(16, 4096, 1024)]
+ROWS = 2048
+
+
+def _dq_f32(values, query, upstream, scale, *, one_pass):
+    from attnres import _native
+    s, n, d = values.shape
+    r = query.numel()
+    out = torch.empty(n, d, device="cuda", dtype=BF16)
+    residual = torch.empty(n, d, device="cuda", dtype=torch.int16) if one_pass else None
+    logits = torch.empty(s, n, device="cuda", dtype=torch.float32)
+    stats = torch.empty(2, n, device="cuda", dtype=torch.float32)
+    dv = torch.empty_like(values)
+    rows = _native.dq_workspace_rows(n, s, d, r, 0)
+    partials = torch.empty(rows, r, device="cuda", dtype=torch.float32)
+    dq = torch.empty(r, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    step = n * d * 2
+    src = [values.data_ptr() + i * step for i in range(s)]
+    flags = _native.FLAG_PREFER_STREAM if one_pass else 0
+    saved = dict(out_ptr=out.data_ptr(), residual_ptr=residual.data_ptr()) if one_pass else {}
+    _native.forward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, scale,
+                    out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream,
+                    residual_ptr=saved.get("residual_ptr"))
+    _native.backward(src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, scale,
+                     upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
+                     [dv.data_ptr() + i * step for i in range(s)], [d] * s,
+                     partials.data_ptr(), rows, None, dq.data_ptr(), flags, stream, **saved)
+    torch.cuda.synchronize()
+    return dq
+
+
+@pytest.mark.parametrize("shape", SWEEP, ids=lambda s: "x".join(map(str, s)))
+def test_fp32_query_gradient_against_the_float64_closed_form(shape):
+    """Relative L2 distance of the FP32 query gradient from the float64 closed form: a few
+    FP32 roundings for both kernel families, and the one-pass kernel no worse than twice
+    the two-pass kernels (they differ only in how delta is formed)."""
+    sources, width, rank = shape
+    scale = 1.0 if rank == width else rank ** -0.5
+    generator = torch.Generator(device="cuda").manual_seed(20260827 + sources + width)
+    values = torch.randn(sources, ROWS, width, device="cuda", dtype=BF16, generator=generator)
+    query = (torch.randn(rank, device="cuda", generator=generator) * 0.02).to(BF16)
+    upstream = torch.randn(ROWS, width, device="cuda", dtype=BF16, generator=generator)
+    exact = ao.closed_form_dquery(values, query, upstream, scale=scale)
+    norm = float(torch.linalg.vector_norm(exact))
+
+    def distance(dq):
+        return float(torch.linalg.vector_norm(dq.double() - exact)) / norm
+
+    two_pass = distance(_dq_f32(values, query, upstream, scale, one_pass=False))
+    one_pass = distance(_dq_f32(values, query, upstream, scale, one_pass=True))
+    print(f"dq_f32 relative-L2 vs float64  S={sources} D={width} R={rank}: "
+          f"two-pass {two_pass:.3e}  one-pass {one_pass:.3e}")
+    assert two_pass < 5e-6, two_pass
+    assert one_pass < 5e-6, one_pass
+    assert one_pass <= 2.0 * two_pass + 2e-7, (one_pass, two_pass)
+
+
+def test_error_no_worse_than_the_reference_triton_kernels():
+    """out, dvalues and dquery of this library against the oracle, next to the reference's
+    Triton kernels on the same inputs (tests/triton_parity.py states the bounds), and the two
+    implementations against each other inside rtol = atol = 0.05."""
+    if not (ROOT / "baseline" / "_ref" / "attnres").exists():
+        pytest.skip("the reference is not installed under baseline/_ref")
+    done = subprocess.run([sys.executable, str(ROOT / "tests" / "triton_parity.py"), "--cells",
+                           "quick", "--rows", str(ROWS)], capture_output=True, text=True,
+                          timeout=1500)
+    if done.returncode != 0:
+        if "triton" in done.stderr.lower() and "import" in done.stderr.lower():
+            pytest.skip("the reference's Triton kernels do not import here: " + done.stderr[-300:])
+        pytest.fail(done.stderr[-3000:])
+    report = json.loads(done.stdout.strip().splitlines()[-1])
+    if "unavailable" in report:
+        pytest.skip(report["unavailable"])
+    failures = []
+    for cell in report["cells"]:
+        for name in ("out", "dvalues", "dquery"):
+            entry = cell[name]
+            print(f"S={cell['S']} D={cell['D']} R={cell['R']} {name}: Triton "
+                  f"{entry['triton']['max_abs']:.3g}/{entry['triton']['relative_l2']:.2e}  ours "
+                  f"{entry['ours']['max_abs']:.3g}/{entry['ours']['relative_l2']:.2e}  bound "
+                  f"{entry['bound']['max_abs']:.3g}/{entry['bound']['relative_l2']:.2e}")
+            if not entry["within_bound"] or not entry["agree_rtol_atol_0.05"]:
+                failures.append((cell["S"], cell["D"], cell["R"], name, entry))
+    assert not failures, failures

@@ -35,6 +35,10 @@ def test_bench_algorithmic_bytes_and_peak():
     assert forward + backward == 16384 * 1220608          # the survey's worked example
     peak, kind = bench.measured_peak_gbs()
     assert peak > 1000 and kind in ("measured", "fallback")
-    ratio = bench.traffic_ratio()
-    assert ratio is None or 0.5 < ratio < 2.0
+    ratios = bench.traffic_ratios()
+    assert ratios and all(0.5 < ratio < 2.0 for ratio in ratios.values())
+    assert set(ratios) <= {"stream", "stash", "ring"}
     assert json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())["backward"]
+    assert bench.backward_family(2, False) == "ring"
+    assert bench.backward_family(9, False) == "stash"
+    assert bench.backward_family(49, True) == "stream"

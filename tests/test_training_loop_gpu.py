@@ -60,3 +60,6 @@ def test_training_loop_follows_the_oracle_and_reduces_the_loss(as_list):
         assert abs(a - b) <= 0.05 * abs(b) + 1e-3, (mine, reference)
     for module in ours.queries:
         assert module.query.dtype == torch.float32 and module.query.grad.dtype == torch.float32
+    # what a training loop should do at a step boundary: no kernel gave up a bounded wait
+    from attnres import _native
+    assert _native.error_flag() == 0

@@ -32,7 +32,13 @@ def _both_backwards(values, query, upstream, flags):
     step = n * d * 2
     src = [values.data_ptr() + i * step for i in range(s)]
     table = (src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, 0.5)
-    _native.forward(*table, out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream)
+    # With the one-pass kernel asked for, the forward also saves its output's residual and
+    # both backwards are handed the pair.
+    one_pass = bool(flags & _native.FLAG_PREFER_STREAM)
+    residual = torch.empty(n, d, device="cuda", dtype=torch.int16) if one_pass else None
+    saved = dict(out_ptr=out.data_ptr(), residual_ptr=residual.data_ptr()) if one_pass else {}
+    _native.forward(*table, out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), flags, stream,
+                    residual_ptr=saved.get("residual_ptr"))
 
     def outputs():
         grads = torch.full((s, n, d), float("nan"), device="cuda", dtype=BF16)
@@ -45,17 +51,17 @@ def _both_backwards(values, query, upstream, flags):
     want_dv, want_dq, want_dq32, ptrs = outputs()
     _native.backward(*table, upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
                      ptrs, [d] * s, workspace.data_ptr(), rows, want_dq.data_ptr(),
-                     want_dq32.data_ptr(), flags, stream)
+                     want_dq32.data_ptr(), flags, stream, **saved)
     got_dv, got_dq, got_dq32, ptrs = outputs()
     status = _native.backward_static_scratch(
         *table, upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(), ptrs, [d] * s,
-        got_dq.data_ptr(), got_dq32.data_ptr(), flags, stream)
+        got_dq.data_ptr(), got_dq32.data_ptr(), flags, stream, **saved)
     assert status == 0, _native.status_text(status)
     torch.cuda.synchronize()
     return (want_dv, want_dq, want_dq32), (got_dv, got_dq, got_dq32)
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["auto", "generic"])
+@pytest.mark.parametrize("flags", [0, 1, 2], ids=["auto", "generic", "one-pass"])
 def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row(flags):
     # Two different problems back to back: the second call finds the first one's partial
     # sums in the shared array and must not be affected by them.
@@ -90,3 +96,31 @@ def test_static_scratch_refuses_shapes_beyond_the_array_without_launching():
     assert status == _native.ERR_STATIC_SCRATCH
     assert "scratch" in _native.status_text(status)
     assert bool((grads == 3.0).all()) and bool((dq == 3.0).all()), "a refused call wrote output"
+
+
+def test_static_scratch_backward_without_query_gradient_needs_no_scratch():
+    """Value gradients only: the call uses no scratch, so a shape whose query-gradient partials
+    would not fit the array is served all the same."""
+    from attnres import _native
+    s, n, d, r = 2, 1500, 4096, 4096
+    assert _native.dq_workspace_rows(n, s, d, r, 0) * r > _native.STATIC_SCRATCH_FLOATS
+    values, query, upstream = _case(s, n, d, r, 5)
+    out = torch.empty(n, d, device="cuda", dtype=BF16)
+    logits = torch.empty(s, n, device="cuda", dtype=torch.float32)
+    stats = torch.empty(2, n, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    step = n * d * 2
+    src = [values.data_ptr() + i * step for i in range(s)]
+    table = (src, [d] * s, [1] * s, s, n, d, r, query.data_ptr(), 1, 2**-23, 0.5)
+    _native.forward(*table, out.data_ptr(), d, logits.data_ptr(), stats.data_ptr(), 0, stream)
+    want = torch.empty_like(values)
+    got = torch.full_like(values, float("nan"))
+    _native.backward(*table, upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
+                     [want.data_ptr() + i * step for i in range(s)], [d] * s, None, 0, None, None,
+                     0, stream)
+    status = _native.backward_static_scratch(
+        *table, upstream.data_ptr(), d, 1, logits.data_ptr(), stats.data_ptr(),
+        [got.data_ptr() + i * step for i in range(s)], [d] * s, None, None, 0, stream)
+    torch.cuda.synchronize()
+    assert status == 0, _native.status_text(status)
+    assert torch.equal(got, want)
