@@ -422,8 +422,9 @@ extern "C" int attnres_b200_backward(
   }
   if (st != ATTNRES_B200_OK) return st;
   if (want_dq) {
-    dq_reduce_kernel<<<(R + 31) / 32, 256, 0, cs>>>(dq_partials, grid, R,
-                                                    static_cast<__nv_bfloat16*>(dq_bf16), dq_f32);
+    dq_reduce_kernel<<<(R + kDqReduceColumns - 1) / kDqReduceColumns,
+                       kDqReduceColumns * kDqReduceGroups, 0, cs>>>(
+        dq_partials, grid, R, static_cast<__nv_bfloat16*>(dq_bf16), dq_f32);
     if (cudaGetLastError() != cudaSuccess) return ATTNRES_B200_ERR_CUDA;
   }
   return ATTNRES_B200_OK;

@@ -151,15 +151,10 @@ bwd_ring_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ Bwd
     const int c = gl + j * L;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      float lo = 0.f, hi = 0.f;
-      if (tail_ok(j)) {
-        const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
-        lo = __bfloat162float(p.query[r * p.query_stride]);
-        hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
-      }
-      q2[j][k] = make_float2(lo, hi);
+      q2[j][k] = make_float2(0.f, 0.f);
       dq2[j][k] = make_float2(0.f, 0.f);
     }
+    if (tail_ok(j)) load_query_chunk(p.query, p.query_stride, c - c0, q2[j]);
   }
 
   const int64_t total_groups = (int64_t)gridDim.x * GROUPS;

@@ -362,15 +362,10 @@ bwd_tma_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ BwdP
     own_tail[j] = FULL ? true : (own_valid[j] && chunk_base + own_chunk[j] >= c0);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      float lo = 0.f, hi = 0.f;
-      if (own_tail[j]) {
-        const int64_t r = (int64_t)(chunk_base + own_chunk[j] - c0) * 8 + 2 * k;
-        lo = __bfloat162float(p.query[r * p.query_stride]);
-        hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
-      }
-      q2[j][k] = make_float2(lo, hi);
+      q2[j][k] = make_float2(0.f, 0.f);
       dq2[j][k] = make_float2(0.f, 0.f);
     }
+    if (own_tail[j]) load_query_chunk(p.query, p.query_stride, chunk_base + own_chunk[j] - c0, q2[j]);
   }
   // Sweep-1 ownership: slice `my_part` of the columns, sources my_first, my_first + step, ...
   const int my_part = warp % NP, my_first = warp / NP, my_step = WT / NP;

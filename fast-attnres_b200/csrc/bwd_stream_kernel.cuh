@@ -178,15 +178,10 @@ bwd_stream_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ B
     const int c = gl + j * L;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      float lo = 0.f, hi = 0.f;
-      if (tail_ok(j)) {
-        const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
-        lo = __bfloat162float(p.query[r * p.query_stride]);
-        hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
-      }
-      q2[j][k] = make_float2(lo, hi);
+      q2[j][k] = make_float2(0.f, 0.f);
       dq2[j][k] = make_float2(0.f, 0.f);
     }
+    if (tail_ok(j)) load_query_chunk(p.query, p.query_stride, c - c0, q2[j]);
   }
 
   const int64_t total_groups = (int64_t)gridDim.x * GROUPS;
@@ -472,9 +467,10 @@ inline int launch_bwd_stream_variant(const BwdParams& p, const BwdStreamPlan& pl
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
 }
 
-// Which switches win was measured per group size on B200 (N = 16384, S = 9..97, GB/s of
-// algorithmic bytes at S = 49, best against worst combination):
-//   G = 1 (D = 1024): all three on, 5141 against 3484;   G = 2 (D = 2048): SR + ZE, 6186 / 5375;
+// Which switches win was measured per group size on B200 (N = 16384, GB/s of algorithmic
+// bytes at S = 49, best against worst combination):
+//   G = 1 (D = 1024): all three on, 5109 against 3462;   G = 2 (D = 2048): SR alone, 6367 / 5457
+//   (SR + ZE, the best before the saved output became an exact FP32 pair, fell to 5578);
 //   G = 4 (D = 4096): none, 6336 / 5393 (SR alone costs 14 %);   G = 8 (D = 8192): SR + tail, 6342 / 5489.
 // The accumulating instances use the same choice.
 template <int G, bool ACC>
@@ -482,7 +478,7 @@ inline int launch_bwd_stream_instance(const BwdParams& p, const BwdStreamPlan& p
                                       cudaStream_t stream) {
   const bool full = p.D / 8 == G * 32 * kRingChunks && plan.stages == kRingStaticStages;
   if (!full) return launch_bwd_stream_variant<G, false, -1, false, false, ACC>(p, plan, grid, stream);
-  constexpr bool SR = G != 4, ZE = G <= 2;
+  constexpr bool SR = G != 4, ZE = G == 1;
   constexpr int TAIL0 = (G == 1 || G == 8) ? 0 : -1;
   if (TAIL0 == 0 && p.R == p.D)
     return launch_bwd_stream_variant<G, true, TAIL0, SR, ZE, ACC>(p, plan, grid, stream);

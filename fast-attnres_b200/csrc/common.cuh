@@ -89,34 +89,30 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // The saved output.  The forward rounds its FP32 result to BF16 (`out`) and, when asked, also
-// keeps what the rounding dropped, as one signed 16-bit integer per element:
-//     low = float_bits(result) - (bf16_bits(out) << 16)            (in -32768 .. 32768)
-// Round-to-nearest moves the upper half of the FP32 pattern by at most one step, so the
-// difference fits 16 bits except for the tie that rounds DOWN to even (+32768), which is
-// stored as 32767 (one FP32 ulp off, one element in 2^17).  The backward gets the FP32
-// result back with an integer add, so `out` + `low` is a full FP32 copy of the output in the
-// space of two BF16 rows.  (The reference saves a separate FP32 copy,
-// src/attnres/_kernels/fixed_tail.py:917-919.)
+// keeps what the rounding dropped, as one unsigned 16-bit integer per element (offset binary):
+//     low = float_bits(result) - (bf16_bits(out) << 16) + 0x8000          (in 0 .. 0x10000)
+// Round-to-nearest moves the upper half of the FP32 pattern by at most one step, so the value
+// fits 16 bits except for the tie that rounds DOWN to even (0x10000), which is stored as
+// 0xffff (one FP32 ulp off, one element in 2^17).  The backward gets the FP32 result back by
+// placing the two halves side by side and subtracting 0x8000, so `out` + `low` is a full FP32
+// copy of the output in the space of two BF16 rows.  (The reference saves a separate FP32
+// copy, src/attnres/_kernels/fixed_tail.py:917-919.)
 //
 // Packed form: `hi` holds two BF16 outputs, the returned word their two 16-bit remainders.
 __device__ __forceinline__ uint32_t split_low16x2(float x0, float x1, uint32_t hi) {
-  int d0 = (int)(__float_as_uint(x0) - (hi << 16));
-  int d1 = (int)(__float_as_uint(x1) - (hi & 0xffff0000u));
-  d0 = min(d0, 32767);
-  d1 = min(d1, 32767);
-  return __byte_perm((uint32_t)d0, (uint32_t)d1, 0x5410);
+  const uint32_t d0 = min(__float_as_uint(x0) - (hi << 16) + 0x8000u, 0xffffu);
+  const uint32_t d1 = min(__float_as_uint(x1) - (hi & 0xffff0000u) + 0x8000u, 0xffffu);
+  return __byte_perm(d0, d1, 0x5410);
 }
 
 __device__ __forceinline__ unsigned short split_low16(float x, unsigned short hi) {
-  int d = (int)(__float_as_uint(x) - ((uint32_t)hi << 16));
-  return (unsigned short)min(d, 32767);
+  return (unsigned short)min(__float_as_uint(x) - ((uint32_t)hi << 16) + 0x8000u, 0xffffu);
 }
 
 // Inverse of split_low16x2: the two FP32 results from the packed BF16 pair and remainders.
 __device__ __forceinline__ float2 join_low16x2(uint32_t hi, uint32_t low) {
-  const uint32_t x0 = (hi << 16) + (uint32_t)(int)(short)(low & 0xffffu);
-  const uint32_t x1 = (hi & 0xffff0000u) + (uint32_t)((int)low >> 16);
-  return make_float2(__uint_as_float(x0), __uint_as_float(x1));
+  return make_float2(__uint_as_float(__byte_perm(low, hi, 0x5410) - 0x8000u),
+                     __uint_as_float(__byte_perm(low, hi, 0x7632) - 0x8000u));
 }
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
@@ -137,6 +133,25 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   r.z = pack_bf16x2(f[4], f[5]);
   r.w = pack_bf16x2(f[6], f[7]);
   return r;
+}
+
+// The eight query values of tail chunk `chunk` (elements 8*chunk .. 8*chunk+7) as four FP32
+// pairs: one 16-byte load when the query is contiguous and aligned, element loads otherwise.
+__device__ __forceinline__ void load_query_chunk(const __nv_bfloat16* query, int64_t stride,
+                                                 int chunk, float2* q) {
+  if (stride == 1 && (reinterpret_cast<uintptr_t>(query) & 15u) == 0) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(query) + chunk);
+    q[0] = make_float2(bf16x2_lo(raw.x), bf16x2_hi(raw.x));
+    q[1] = make_float2(bf16x2_lo(raw.y), bf16x2_hi(raw.y));
+    q[2] = make_float2(bf16x2_lo(raw.z), bf16x2_hi(raw.z));
+    q[3] = make_float2(bf16x2_lo(raw.w), bf16x2_hi(raw.w));
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t r = (int64_t)chunk * 8 + 2 * k;
+      q[k] = make_float2(__bfloat162float(query[r * stride]), __bfloat162float(query[(r + 1) * stride]));
+    }
+  }
 }
 
 // Butterfly sum: every lane ends with the same value, in an order that depends

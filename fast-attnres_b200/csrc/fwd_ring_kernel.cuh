@@ -189,15 +189,8 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     in_row[j] = STATIC_TAIL ? true : c < CH;
     in_tail[j] = STATIC_TAIL ? (j >= TAIL0) : (c < CH && c >= c0);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float lo = 0.f, hi = 0.f;
-      if (in_tail[j]) {
-        const int64_t r = (int64_t)(c - c0) * 8 + 2 * k;
-        lo = __bfloat162float(p.query[r * p.query_stride]);
-        hi = __bfloat162float(p.query[(r + 1) * p.query_stride]);
-      }
-      q2[j][k] = make_float2(lo, hi);
-    }
+    for (int k = 0; k < 4; ++k) q2[j][k] = make_float2(0.f, 0.f);
+    if (in_tail[j]) load_query_chunk(p.query, p.query_stride, c - c0, q2[j]);
   }
 
   const int64_t total_groups = (int64_t)gridDim.x * GROUPS;

@@ -335,28 +335,47 @@ bwd_generic_kernel(const __grid_constant__ BwdParams p) {
   }
 }
 
-// Second stage of the query gradient: column sums of the [rows, R] partials in
-// a fixed order (8 interleaved row groups, then the groups in index order), so
-// the result is bit-identical from call to call.  The reference reduces a
-// [N, R] buffer with ceil(R/32) programs (src/attnres/_kernels/fixed_tail.py:875-899).
-__global__ void __launch_bounds__(256)
+// Second stage of the query gradient: column sums of the [rows, R] partials in a fixed
+// order, so the result is bit-identical from call to call.  A CTA owns 16 columns (one
+// 64-byte segment of every row); its 32 row groups each add every 32nd row, four rows at a
+// time into four independent FP64 sums (so several loads are in flight per thread), and the
+// groups are then added in index order.  Summing in FP64 means this stage adds no rounding
+// of its own: the result is the FP32 rounding of the exact sum of the partials.  The
+// reference reduces a [N, R] buffer with ceil(R/32) programs
+// (src/attnres/_kernels/fixed_tail.py:875-899).
+constexpr int kDqReduceColumns = 16;
+constexpr int kDqReduceGroups = 32;
+
+__global__ void __launch_bounds__(kDqReduceColumns * kDqReduceGroups)
 dq_reduce_kernel(const float* __restrict__ partials, int rows, int R,
                  __nv_bfloat16* __restrict__ dq_bf16, float* __restrict__ dq_f32) {
-  __shared__ double sm[8][33];
-  const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
-  const int r = blockIdx.x * 32 + col;
-  // The partial rows are summed in FP64, so this stage adds no rounding of its own: the
-  // result is the FP32 rounding of the exact sum of the partials.
+  __shared__ double sm[kDqReduceGroups][kDqReduceColumns + 1];
+  const int col = threadIdx.x % kDqReduceColumns, grp = threadIdx.x / kDqReduceColumns;
+  const int r = blockIdx.x * kDqReduceColumns + col;
   double sum = 0.0;
   if (r < R) {
-    for (int row = grp; row < rows; row += 8) sum += (double)partials[(int64_t)row * R + r];
+    const float* column = partials + r;
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    int row = grp;
+    for (; row + 3 * kDqReduceGroups < rows; row += 4 * kDqReduceGroups) {
+      const float a = column[(int64_t)row * R];
+      const float b = column[(int64_t)(row + kDqReduceGroups) * R];
+      const float c = column[(int64_t)(row + 2 * kDqReduceGroups) * R];
+      const float d = column[(int64_t)(row + 3 * kDqReduceGroups) * R];
+      s0 += (double)a;
+      s1 += (double)b;
+      s2 += (double)c;
+      s3 += (double)d;
+    }
+    for (; row < rows; row += kDqReduceGroups) s0 += (double)column[(int64_t)row * R];
+    sum = (s0 + s1) + (s2 + s3);
   }
   sm[grp][col] = sum;
   __syncthreads();
   if (grp == 0 && r < R) {
     double total = 0.0;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) total += sm[k][col];
+    for (int k = 0; k < kDqReduceGroups; ++k) total += sm[k][col];
     const float rounded = (float)total;
     if (dq_f32 != nullptr) dq_f32[r] = rounded;
     if (dq_bf16 != nullptr) dq_bf16[r] = __float2bfloat16_rn(rounded);

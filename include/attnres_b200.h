@@ -99,12 +99,12 @@ const char* attnres_b200_status_string(int status);
  *                      [S,N,D] tensor is passed as base + s*stride(0))
  *   query              device BF16 [R], element stride `query_stride`
  *   out                device BF16 [N,D], row stride `out_row_stride`, feature stride 1
- *   out_residual       optional device int16 [N,D] contiguous: what the BF16 rounding of `out`
- *                      dropped, so that the pair is a full FP32 copy of the result in the
- *                      space of two BF16 rows:
- *                        float_bits(result) = (bf16_bits(out) << 16) + out_residual
- *                      (signed add; exact except for the one-in-2^17 tie that rounds down,
- *                      which is one FP32 ulp off).  Ask attnres_b200_wants_output_residual
+ *   out_residual       optional device uint16 [N,D] contiguous: what the BF16 rounding of
+ *                      `out` dropped, so that the pair is a full FP32 copy of the result in
+ *                      the space of two BF16 rows:
+ *                        float_bits(result) = ((bf16_bits(out) << 16) | out_residual) - 0x8000
+ *                      (exact except for the one-in-2^17 tie that rounds down, which is one
+ *                      FP32 ulp off).  Ask attnres_b200_wants_output_residual
  *                      whether the backward of this shape profits from it; NULL skips it.
  *                      The reference saves a separate FP32 copy of the output
  *                      (fixed_tail.py:917-919); its backward and this one then form

@@ -123,10 +123,12 @@ def closed_form_dquery(values: torch.Tensor, query: torch.Tensor, upstream: torc
 
 
 def join_saved_output(out: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-    """The FP32 result the forward kernels computed, from the BF16 output and the int16
-    residual they save with it: float_bits = (bf16_bits(out) << 16) + residual."""
+    """The FP32 result the forward kernels computed, from the BF16 output and the 16-bit
+    residual they save with it (held in an int16 tensor, read as unsigned):
+    float_bits = ((bf16_bits(out) << 16) | residual) - 0x8000."""
     high = out.contiguous().view(torch.int16).to(torch.int32) << 16
-    return (high + residual.to(torch.int32)).view(torch.float32)
+    low = residual.to(torch.int32) & 0xFFFF
+    return ((high | low) - 0x8000).view(torch.float32)
 
 
 def bf16_bits(tensor: torch.Tensor) -> np.ndarray:

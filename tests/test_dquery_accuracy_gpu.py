@@ -74,9 +74,10 @@ def test_fp32_query_gradient_against_the_float64_closed_form(shape):
     one_pass = distance(_dq_f32(values, query, upstream, scale, one_pass=True))
     print(f"dq_f32 relative-L2 vs float64  S={sources} D={width} R={rank}: "
           f"two-pass {two_pass:.3e}  one-pass {one_pass:.3e}")
-    assert two_pass < 5e-6, two_pass
-    assert one_pass < 5e-6, one_pass
-    assert one_pass <= 2.0 * two_pass + 2e-7, (one_pass, two_pass)
+    # measured on B200: 1.3e-7 .. 5.1e-7 (two passes), 1.7e-7 .. 3.5e-7 (one pass)
+    assert two_pass < 2e-6, two_pass
+    assert one_pass < 2e-6, one_pass
+    assert one_pass <= 2.0 * two_pass + 1e-7, (one_pass, two_pass)
 
 
 def test_error_no_worse_than_the_reference_triton_kernels():
@@ -86,7 +87,7 @@ def test_error_no_worse_than_the_reference_triton_kernels():
     if not (ROOT / "baseline" / "_ref" / "attnres").exists():
         pytest.skip("the reference is not installed under baseline/_ref")
     done = subprocess.run([sys.executable, str(ROOT / "tests" / "triton_parity.py"), "--cells",
-                           "quick", "--rows", str(ROWS)], capture_output=True, text=True,
+                           "all", "--rows", str(ROWS)], capture_output=True, text=True,
                           timeout=1500)
     if done.returncode != 0:
         if "triton" in done.stderr.lower() and "import" in done.stderr.lower():
