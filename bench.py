@@ -658,6 +658,139 @@ def run_e2e(args, cells, device, distributed, world=1) -> dict:
     return {"ms_per_step": ms_per_step, "h2d": h2d, "d2h": d2h, "steps": steps, "pcie": pcie}
 
 
+MODEL_WORKLOADS = {
+    # the reference's 24-layer Full-schedule training step (its fourth benchmark configuration)
+    "config4": dict(layers=24, width=1024, heads=16, ffn=4096, vocab=32000, sequence=2048,
+                    rank=None, mode="full", block_layers=1, layout="list", batch_per_gpu=8,
+                    global_batch=None, parameters="fp32 + bf16 autocast"),
+    # its 8-GPU Block-schedule configuration: D = 4096, blocks of 4 layers (S <= 7), R = 1024
+    "config5": dict(layers=24, width=4096, heads=32, ffn=16384, vocab=32000, sequence=4096,
+                    rank=1024, mode="block", block_layers=4, layout="list", batch_per_gpu=4,
+                    global_batch=32, parameters="bf16"),
+}
+
+
+def run_model_workload(args, rank: int, world: int, local_rank: int) -> None:
+    """`--workload config4|config5`: one training step of the benchmark language model
+    (baseline/lm.py) with this library's reads, data-parallel over the ranks.
+
+    Every rank holds a replica and its own microbatches (positions are sharded by the batch
+    split, so the reads need no communication); DistributedDataParallel all-reduces the weight
+    gradients and the [R] query gradients over NCCL in buckets that overlap the backward.
+    With a fixed global batch (config5: 32 sequences) a rank runs 32 / (4 world) microbatches
+    per step and synchronises on the last one.  Timed: K whole steps (zero_grad, forward,
+    cross entropy, backward, all-reduce, fused AdamW) between barriers, CUDA events, max over
+    ranks.  The step is also timed with the all-reduce switched off (`no_sync`), which shows
+    how much of it the overlap does not hide."""
+    import contextlib
+    import torch.distributed as dist
+    from attnres import _native, attnres
+    from baseline import lm
+    spec = dict(MODEL_WORKLOADS[args.workload])
+    if args.layers:
+        spec["layers"] = args.layers
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    batch_per_gpu = spec.pop("batch_per_gpu")
+    global_batch = spec.pop("global_batch")
+    parameters = spec.pop("parameters")
+    accumulation = 1
+    if global_batch and not args.weak:
+        accumulation = max(1, global_batch // (batch_per_gpu * world))
+    config = lm.LMConfig(**spec)
+    torch.manual_seed(SEED)            # the same initial weights on every rank
+    with torch.device(device):
+        model = lm.CausalLM(config, attnres)
+    if parameters == "bf16":
+        model = model.to(torch.bfloat16)
+    wrapped = model
+    if distributed:
+        wrapped = torch.nn.parallel.DistributedDataParallel(
+            model, device_ids=[local_rank], gradient_as_bucket_view=True, bucket_cap_mb=256)
+    runner = torch.compile(wrapped, fullgraph=False) if args.compile else wrapped
+    optimizer = lm.make_optimizer(model, capturable=False)
+    generator = torch.Generator(device=device).manual_seed(SEED + 1 + rank)
+    shape = (batch_per_gpu * accumulation, config.sequence)
+    tokens = torch.randint(config.vocab, shape, device=device, generator=generator)
+    targets = torch.randint(config.vocab, shape, device=device, generator=generator)
+
+    def sync_context(last):
+        if distributed and not last:
+            return wrapped.no_sync()
+        return contextlib.nullcontext()
+
+    def never_sync(last):
+        return wrapped.no_sync() if distributed else contextlib.nullcontext()
+
+    def timed(steps, context):
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        loss = None
+        for _ in range(steps):
+            loss = lm.training_step(runner, optimizer, tokens, targets, accumulation=accumulation,
+                                    sync_context=context)
+        stop.record()
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        if distributed:
+            worst = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            ms = float(worst.item())
+        return ms, float(loss)
+
+    warmup = max(args.warmup, 1)
+    timed(warmup, sync_context)
+    with ClockSampler(local_rank) as clocks:
+        ms_per_step, loss = timed(args.steps, sync_context)
+    quiet_ms = None
+    if distributed:
+        quiet_ms, _ = timed(max(1, min(args.steps, 2)), never_sync)
+    torch.cuda.synchronize()
+    gave_up = _native.error_flag()
+    if rank != 0:
+        return
+    rows = batch_per_gpu * config.sequence            # positions per microbatch and rank
+    tokens_per_step = rows * accumulation * world
+    parameters_count = sum(p.numel() for p in model.parameters())
+    grad_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    query_grad_bytes = sum(q.numel() * q.element_size() for q in model.queries)
+    counts = lm.read_source_counts(config)
+    line = {
+        "metric": "train_step_tokens_per_s", "value": tokens_per_step / (ms_per_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak" if (args.weak or not global_batch) else "strong (fixed global batch)",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}_{config.mode}_schedule_L{config.layers}_D{config.width}"
+                               f"_R{config.rank}_seq{config.sequence}",
+                   "layers": config.layers, "full_layers": MODEL_WORKLOADS[args.workload]["layers"],
+                   "sequences_per_gpu_microbatch": batch_per_gpu,
+                   "microbatches_per_gpu_step": accumulation,
+                   "global_batch_sequences": batch_per_gpu * accumulation * world,
+                   "parameters": parameters, "parameter_count": parameters_count,
+                   "optimizer": "AdamW fused lr 3e-4 betas 0.9/0.95 wd 0.1",
+                   "compiled": bool(args.compile),
+                   "parallelism": f"data parallel x{world} (DistributedDataParallel, NCCL, "
+                                  "256 MB buckets overlapping the backward)",
+                   "reads_per_microbatch": len(counts), "sources_per_read": sorted(set(counts)),
+                   "attnres_algorithmic_gb_per_gpu_step":
+                       lm.attnres_algorithmic_bytes(config, rows) * accumulation / 1e9},
+        "collective": {"gradient_bytes_all_reduced_per_step": grad_bytes if distributed else 0,
+                       "of_which_query_gradients": query_grad_bytes if distributed else 0,
+                       "ms_per_step_without_all_reduce": quiet_ms,
+                       "exposed_ms_per_step": None if quiet_ms is None else ms_per_step - quiet_ms},
+        "loss": loss, "peak_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+        "clocks": clocks.summary(), "wait_gave_up_flag": gave_up,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_single_cell(args) -> None:
     """`--cell S,D[,R]`: one shape, eager launches through the C ABI, per-call CUDA-event
     times.  This is the small case the ncu captures under profiles/ were taken on."""
@@ -782,6 +915,16 @@ def main() -> None:
                         help="profiling runs: leave out the host-buffer end-to-end leg")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="profiling runs: leave out the CPU-oracle leg")
+    parser.add_argument("--workload", choices=("sweep", *MODEL_WORKLOADS), default="sweep",
+                        help="sweep (default): the operator sweep; config4 / config5: a training "
+                             "step of the benchmark language model, data-parallel over the ranks")
+    parser.add_argument("--layers", type=int, default=0,
+                        help="model workloads: fewer layers than the configuration names")
+    parser.add_argument("--weak", action="store_true",
+                        help="config5: one microbatch per GPU and step instead of the fixed "
+                             "global batch of 32 sequences")
+    parser.add_argument("--compile", action="store_true",
+                        help="model workloads: run the model under torch.compile")
     parser.add_argument("--cell", default=None, help="S,D[,R]: time one shape instead of the sweep")
     parser.add_argument("--rows", type=int, default=ROWS, help="rows of the --cell run")
     parser.add_argument("--generic", action="store_true", help="--cell: force the generic kernels")
@@ -813,7 +956,10 @@ def main() -> None:
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_gpu_arm(args, rank, world, local_rank)
+        if args.workload != "sweep":
+            run_model_workload(args, rank, world, local_rank)
+        else:
+            run_gpu_arm(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

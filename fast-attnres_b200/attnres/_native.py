@@ -32,6 +32,13 @@ SIGNATURES = {
         c_void_p, c_int64, c_float, c_float,
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
         c_uint32, c_void_p]),
+    "attnres_b200_forward_layer_norm": (c_int32, [
+        _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
+        c_int32, c_int64, c_int32, c_int32,
+        c_void_p, c_int64, c_float, c_float,
+        c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+        c_uint32, c_void_p]),
     "attnres_b200_wants_output_residual": (c_int32, [c_int32, c_int32, c_int32]),
     "attnres_b200_backward_static_scratch": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
@@ -103,6 +110,18 @@ def forward(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_st
         S, N, D, R, query_ptr, query_stride, eps, scale,
         out_ptr, out_row_stride, residual_ptr, logits_ptr, stats_ptr, flags, stream)
     check(status, "attnres_b200_forward")
+
+
+def forward_layer_norm(src_ptrs, row_strides, feat_strides, S, N, D, R, query_ptr, query_stride,
+                       eps, scale, out_ptr, out_row_stride, logits_ptr, stats_ptr,
+                       weight_ptr, bias_ptr, norm_eps, normed_ptr, norm_stats_ptr, flags, stream,
+                       residual_ptr=None) -> None:
+    status = load().attnres_b200_forward_layer_norm(
+        pointer_array(src_ptrs), int64_array(row_strides), int64_array(feat_strides),
+        S, N, D, R, query_ptr, query_stride, eps, scale,
+        out_ptr, out_row_stride, residual_ptr, logits_ptr, stats_ptr,
+        weight_ptr, bias_ptr, norm_eps, normed_ptr, norm_stats_ptr, flags, stream)
+    check(status, "attnres_b200_forward_layer_norm")
 
 
 def wants_output_residual(S, D, R) -> bool:

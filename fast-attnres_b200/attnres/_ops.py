@@ -181,7 +181,10 @@ def _(values, query, eps, scale):
 def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output: torch.Tensor,
                          logits: torch.Tensor, stats: torch.Tensor, out: torch.Tensor,
                          residual: torch.Tensor, eps: float, scale: float,
-                         need_values: bool, need_query: bool) -> tuple[torch.Tensor, torch.Tensor]:
+                         need_values: bool, need_query: bool, query_grad_fp32: bool
+                         ) -> tuple[torch.Tensor, torch.Tensor]:
+    """`query_grad_fp32`: return the query gradient as the FP32 second-stage sum (for a caller
+    that adds it across ranks before the one rounding to BF16)."""
     _require_cuda_bf16((values, grad_output), query)
     _require_saved_output(out, residual)
     kept, ptrs, row_strides, feat_strides = _packed_table(values)
@@ -193,7 +196,8 @@ def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output:
         step = rows * width * values.element_size()
         grad_ptrs = [grad_values.data_ptr() + s * step for s in range(count)]
     grad_query = _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output,
-                               logits, stats, out, residual, eps, scale, grad_ptrs, need_query)
+                               logits, stats, out, residual, eps, scale, grad_ptrs, need_query,
+                               query_grad_dtype=torch.float32 if query_grad_fp32 else torch.bfloat16)
     # Schema outputs are plain tensors: an unused gradient is a 0-element stand-in.
     if grad_values is None:
         grad_values = values.new_empty((0,))
@@ -204,9 +208,10 @@ def read_packed_backward(values: torch.Tensor, query: torch.Tensor, grad_output:
 
 @read_packed_backward.register_fake
 def _(values, query, grad_output, logits, stats, out, residual, eps, scale, need_values,
-      need_query):
+      need_query, query_grad_fp32):
     return (values.new_empty(values.shape if need_values else (0,)),
-            query.new_empty(query.shape if need_query else (0,)))
+            query.new_empty(query.shape if need_query else (0,),
+                            dtype=torch.float32 if query_grad_fp32 else query.dtype))
 
 
 def _packed_setup(ctx, inputs, output) -> None:
@@ -229,7 +234,7 @@ def _packed_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None, _gra
         return None, None, None, None
     grad_values, grad_query = read_packed_backward(
         values, query, grad_output, logits, stats, out, residual, float(ctx.eps),
-        float(ctx.scale), need_values, need_query)
+        float(ctx.scale), need_values, need_query, False)
     return (grad_values if need_values else None, grad_query if need_query else None, None, None)
 
 
@@ -263,7 +268,9 @@ def _(sources, query, eps, scale):
 def read_sources_backward(sources: list[torch.Tensor], query: torch.Tensor,
                           grad_output: torch.Tensor, logits: torch.Tensor, stats: torch.Tensor,
                           out: torch.Tensor, residual: torch.Tensor,
-                          eps: float, scale: float) -> list[torch.Tensor]:
+                          eps: float, scale: float, query_grad_fp32: bool) -> list[torch.Tensor]:
+    """Returns the S value gradients followed by the query gradient (FP32 second-stage sum
+    when `query_grad_fp32`, else BF16)."""
     _require_cuda_bf16((*sources, grad_output), query)
     _require_saved_output(out, residual)
     kept, ptrs, row_strides, feat_strides = _source_table(sources)
@@ -272,13 +279,15 @@ def read_sources_backward(sources: list[torch.Tensor], query: torch.Tensor,
              for _ in sources]
     grad_query = _run_backward(kept, ptrs, row_strides, feat_strides, shape, query, grad_output,
                                logits, stats, out, residual, eps, scale,
-                               [g.data_ptr() for g in grads], True)
+                               [g.data_ptr() for g in grads], True,
+                               query_grad_dtype=torch.float32 if query_grad_fp32 else torch.bfloat16)
     return [*grads, grad_query]
 
 
 @read_sources_backward.register_fake
-def _(sources, query, grad_output, logits, stats, out, residual, eps, scale):
-    return [source.new_empty(source.shape) for source in sources] + [query.new_empty(query.shape)]
+def _(sources, query, grad_output, logits, stats, out, residual, eps, scale, query_grad_fp32):
+    return [source.new_empty(source.shape) for source in sources] + [
+        query.new_empty(query.shape, dtype=torch.float32 if query_grad_fp32 else query.dtype)]
 
 
 def _sources_setup(ctx, inputs, output) -> None:
@@ -299,7 +308,7 @@ def _sources_backward(ctx, grad_output, _grad_logits=None, _grad_stats=None, _gr
     count = ctx.count
     gradients = read_sources_backward(list(saved[:count]), saved[count], grad_output,
                                       saved[count + 1], saved[count + 2], saved[count + 3],
-                                      saved[count + 4], float(ctx.eps), float(ctx.scale))
+                                      saved[count + 4], float(ctx.eps), float(ctx.scale), False)
     return gradients[:count], gradients[count], None, None
 
 

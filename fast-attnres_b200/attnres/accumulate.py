@@ -17,14 +17,15 @@ Usage::
     out.backward(grad)                                        # buffers[s] += dV_s; query.grad as usual
     torch.autograd.backward(sources, grad_tensors=buffers)    # continue into the producers
 
-The sources get NO gradient through autograd from this call (it is in the buffers).  Eager and
-CUDA-graph use only: the buffers are side effects, which ``torch.compile`` does not trace.
+The sources get NO gradient through autograd from this call (it is in the buffers).  The read
+is a ``torch.library`` operator whose backward operator declares the buffers as mutated
+arguments, so it runs eagerly, under CUDA graphs and under ``torch.compile``.
 """
 from __future__ import annotations
 
 import torch
 
-from . import _native
+from . import _native, _ops
 from ._sources import DEFAULT_EPS, check_packed, check_sources
 
 
@@ -54,50 +55,87 @@ def _check_buffers(buffers, shapes, device) -> None:
             raise ValueError("every source needs its own gradient buffer (buffers overlap)")
 
 
-class _AccumulatingRead(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, query, eps, scale, packed, buffers, overwrite, *sources):
-        from . import _ops
-        if packed:
-            kept, ptrs, rs, fs = _ops._packed_table(sources[0])
-            shape = sources[0].shape[1:]
-        else:
-            kept, ptrs, rs, fs = _ops._source_table(sources)
-            shape = sources[0].shape
-        # The output is always kept with its residual: the accumulating backward of the fast
-        # layout class is the one-pass kernel (other layouts use the generic kernel and ignore it).
-        out, logits, stats, residual = _ops._run_forward(kept, ptrs, rs, fs, shape, query, eps,
-                                                         scale, keep_residual=True)
-        ctx.save_for_backward(query, logits, stats, out, residual, *sources)
-        ctx.eps, ctx.scale, ctx.packed, ctx.buffers = eps, scale, packed, buffers
-        ctx.overwrite = overwrite
-        ctx.set_materialize_grads(False)
-        return out
+# Two torch.library operators: the forward is the plain read (it always keeps the output and
+# its residual: the accumulating backward of the fast layout class is the one-pass kernel);
+# the backward operator declares the buffers as mutated arguments, so a read whose backward
+# accumulates traces under torch.compile like any other in-place custom op.  The buffers ride
+# along the forward operator only to reach its backward; the forward does not touch them.
 
-    @staticmethod
-    def backward(ctx, grad_output):
-        from . import _ops
-        count = len(ctx.saved_tensors) - 5
-        nothing = (None,) * (6 + count)
-        if grad_output is None:
-            return nothing
-        query, logits, stats, out, residual, *sources = ctx.saved_tensors
-        if ctx.packed:
-            values = sources[0]
-            kept, ptrs, rs, fs = _ops._packed_table(values)
-            shape = values.shape[1:]
-            buffer = ctx.buffers[0]
-            step = buffer.stride(0) * buffer.element_size()
-            grad_ptrs = [buffer.data_ptr() + s * step for s in range(values.shape[0])]
-        else:
-            kept, ptrs, rs, fs = _ops._source_table(sources)
-            shape = sources[0].shape
-            grad_ptrs = [b.data_ptr() for b in ctx.buffers]
-        grad_query = _ops._run_backward(kept, ptrs, rs, fs, shape, query, grad_output, logits, stats,
-                                        out, residual, ctx.eps, ctx.scale, grad_ptrs,
-                                        bool(ctx.needs_input_grad[0]),
-                                        extra_flags=0 if ctx.overwrite else _native.FLAG_ACCUMULATE_DV)
-        return (grad_query, *nothing[1:])
+@_ops._custom_op("attnres_b200::accumulate_sources_forward", mutates_args=(), device_types="cuda",
+                 **_ops._LIST_OP_KWARGS)
+def accumulate_sources_forward(sources: list[torch.Tensor], query: torch.Tensor,
+                               buffers: list[torch.Tensor], eps: float, scale: float,
+                               overwrite: bool
+                               ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    _ops._require_cuda_bf16(sources, query)
+    kept, ptrs, rs, fs = _ops._source_table(sources)
+    return _ops._run_forward(kept, ptrs, rs, fs, sources[0].shape, query, eps, scale,
+                             keep_residual=True)
+
+
+@accumulate_sources_forward.register_fake
+def _(sources, query, buffers, eps, scale, overwrite):
+    first = sources[0]
+    rows = _ops._rows(first.shape)
+    return (first.new_empty(first.shape),
+            first.new_empty((len(sources), rows), dtype=torch.float32),
+            first.new_empty((2, rows), dtype=torch.float32),
+            first.new_empty(first.shape, dtype=torch.int16))
+
+
+@_ops._custom_op("attnres_b200::accumulate_sources_backward", mutates_args=("buffers",),
+                 device_types="cuda")
+def accumulate_sources_backward(sources: list[torch.Tensor], query: torch.Tensor,
+                                grad_output: torch.Tensor, logits: torch.Tensor,
+                                stats: torch.Tensor, out: torch.Tensor, residual: torch.Tensor,
+                                buffers: list[torch.Tensor], eps: float, scale: float,
+                                overwrite: bool, need_query: bool) -> torch.Tensor:
+    """buffers[s] += dV_s (or = dV_s with `overwrite`); returns the BF16 query gradient, or a
+    0-element tensor when it is not needed."""
+    _ops._require_cuda_bf16((*sources, grad_output, *buffers), query)
+    kept, ptrs, rs, fs = _ops._source_table(sources)
+    grad_query = _ops._run_backward(kept, ptrs, rs, fs, sources[0].shape, query, grad_output,
+                                    logits, stats, out, residual, eps, scale,
+                                    [b.data_ptr() for b in buffers], need_query,
+                                    extra_flags=0 if overwrite else _native.FLAG_ACCUMULATE_DV)
+    return grad_query if grad_query is not None else query.new_empty((0,))
+
+
+@accumulate_sources_backward.register_fake
+def _(sources, query, grad_output, logits, stats, out, residual, buffers, eps, scale, overwrite,
+      need_query):
+    return query.new_empty(query.shape if need_query else (0,))
+
+
+def _accumulate_setup(ctx, inputs, output) -> None:
+    sources, query, buffers, eps, scale, overwrite = inputs
+    out, logits, stats, residual = output
+    ctx.mark_non_differentiable(logits, stats, residual)
+    ctx.set_materialize_grads(False)
+    ctx.save_for_backward(*sources, query, logits, stats, out, residual)
+    # Not saved tensors: later reads' backwards update the buffers in place before this
+    # read's backward runs, which autograd's version check would take for a bug.
+    ctx.buffers = list(buffers)
+    ctx.count = len(sources)
+    ctx.eps, ctx.scale, ctx.overwrite = eps, scale, overwrite
+
+
+def _accumulate_backward(ctx, grad_output, *_unused):
+    count = ctx.count
+    nothing = ([None] * count, None, [None] * count, None, None, None)
+    if grad_output is None:
+        return nothing
+    saved = ctx.saved_tensors
+    need_query = bool(ctx.needs_input_grad[1])
+    grad_query = accumulate_sources_backward(
+        list(saved[:count]), saved[count], grad_output, saved[count + 1], saved[count + 2],
+        saved[count + 3], saved[count + 4], ctx.buffers, float(ctx.eps), float(ctx.scale),
+        bool(ctx.overwrite), need_query)
+    return ([None] * count, grad_query if need_query else None, [None] * count, None, None, None)
+
+
+torch.library.register_autograd(accumulate_sources_forward, _accumulate_backward,
+                                setup_context=_accumulate_setup)
 
 
 def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float = DEFAULT_EPS,
@@ -108,9 +146,10 @@ def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float 
     them: for the read whose backward runs first in a step, so the buffers need no zeroing.
 
     ``values`` packed ``[S, ..., D]``: ``grad_buffers`` is one contiguous BF16 tensor of the
-    same shape.  ``values`` a list/tuple of ``[..., D]`` sources: ``grad_buffers`` is a list of
-    contiguous BF16 tensors, one per source, each with its source's shape and its own memory.
-    The forward result and the query gradient are those of ``attnres``.
+    same shape (read and updated through its S slices).  ``values`` a list/tuple of ``[..., D]``
+    sources: ``grad_buffers`` is a list of contiguous BF16 tensors, one per source, each with
+    its source's shape and its own memory.  The forward result and the query gradient are
+    those of ``attnres``.
     """
     if isinstance(values, torch.Tensor):
         check_packed(values, query, eps, scale)
@@ -119,16 +158,17 @@ def attnres_accumulate(values, query: torch.Tensor, grad_buffers, *, eps: float 
         if not isinstance(grad_buffers, torch.Tensor):
             raise TypeError("a packed call takes one packed gradient buffer")
         _check_buffers([grad_buffers], [values.shape], values.device)
-        return _AccumulatingRead.apply(query, float(eps), float(scale), True, [grad_buffers],
-                                       bool(overwrite), values)
-    sources = check_sources(values, query, eps, scale)
-    if not sources[0].is_cuda:
-        raise RuntimeError("attnres requires CUDA tensors")
-    if not isinstance(grad_buffers, (list, tuple)):
-        raise TypeError("a list call takes a list of gradient buffers")
-    _check_buffers(list(grad_buffers), [s.shape for s in sources], sources[0].device)
-    return _AccumulatingRead.apply(query, float(eps), float(scale), False, list(grad_buffers),
-                                   bool(overwrite), *sources)
+        sources, buffers = list(values.unbind(0)), list(grad_buffers.unbind(0))
+    else:
+        sources = list(check_sources(values, query, eps, scale))
+        if not sources[0].is_cuda:
+            raise RuntimeError("attnres requires CUDA tensors")
+        if not isinstance(grad_buffers, (list, tuple)):
+            raise TypeError("a list call takes a list of gradient buffers")
+        buffers = list(grad_buffers)
+        _check_buffers(buffers, [s.shape for s in sources], sources[0].device)
+    return accumulate_sources_forward(sources, query, buffers, float(eps), float(scale),
+                                      bool(overwrite))[0]
 
 
 __all__ = ["attnres_accumulate"]

@@ -275,13 +275,24 @@ extern "C" int attnres_b200_error_flag(int32_t* flag, int32_t clear) {
   return ATTNRES_B200_OK;
 }
 
-extern "C" int attnres_b200_forward(
+namespace {
+
+// Optional LayerNorm epilogue of a forward call (all NULL / zero: none).
+struct LayerNormArgs {
+  const float* weight = nullptr;
+  const float* bias = nullptr;
+  float eps = 0.f;
+  void* out = nullptr;
+  float* stats = nullptr;
+};
+
+int forward_impl(
     const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
     int32_t S, int64_t N, int32_t D, int32_t R,
     const void* query, int64_t query_stride,
     float eps, float scale,
     void* out, int64_t out_row_stride, void* out_residual,
-    float* logits, float* stats,
+    float* logits, float* stats, const LayerNormArgs& ln,
     uint32_t flags, void* stream) {
   if (int st = check_shape(S, N, D, R)) return st;
   if (int st = check_scalars(eps, scale)) return st;
@@ -307,8 +318,15 @@ extern "C" int attnres_b200_forward(
   p.out_residual = static_cast<__nv_bfloat16*>(out_residual);
   p.logits = logits;
   p.stats = stats;
+  p.ln_weight = ln.weight;
+  p.ln_bias = ln.bias;
+  p.ln_eps = ln.eps;
+  p.ln_out = static_cast<__nv_bfloat16*>(ln.out);
+  p.ln_stats = ln.stats;
   vec = vec && D % 8 == 0 && aligned16(out) && (N == 1 || out_row_stride % 8 == 0) &&
-        (out_residual == nullptr || aligned16(out_residual));
+        (out_residual == nullptr || aligned16(out_residual)) &&
+        (ln.out == nullptr || (aligned16(ln.out) && (ln.weight == nullptr || aligned16(ln.weight)) &&
+                               (ln.bias == nullptr || aligned16(ln.bias))));
 
   int device = 0, sms = 0;
   if (int st = current_device(&device)) return st;
@@ -321,6 +339,45 @@ extern "C" int attnres_b200_forward(
   const int64_t cap = (int64_t)sms * 16;
   const int grid = (int)(N < cap ? N : cap);
   return dispatch_fwd_generic(p, vec, grid, cs);
+}
+
+}  // namespace
+
+extern "C" int attnres_b200_forward(
+    const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    void* out, int64_t out_row_stride, void* out_residual,
+    float* logits, float* stats,
+    uint32_t flags, void* stream) {
+  return forward_impl(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query, query_stride,
+                      eps, scale, out, out_row_stride, out_residual, logits, stats,
+                      LayerNormArgs{}, flags, stream);
+}
+
+extern "C" int attnres_b200_forward_layer_norm(
+    const void* const* src_ptrs, const int64_t* src_row_stride, const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    void* out, int64_t out_row_stride, void* out_residual,
+    float* logits, float* stats,
+    const float* norm_weight, const float* norm_bias, float norm_eps,
+    void* normed_out, float* norm_stats,
+    uint32_t flags, void* stream) {
+  if (normed_out == nullptr || norm_stats == nullptr) return ATTNRES_B200_ERR_NULL_POINTER;
+  if (!aligned2(normed_out)) return ATTNRES_B200_ERR_MISALIGNED;
+  if (!std::isfinite(norm_eps) || norm_eps < 0.f) return ATTNRES_B200_ERR_BAD_SCALAR;
+  LayerNormArgs ln;
+  ln.weight = norm_weight;
+  ln.bias = norm_bias;
+  ln.eps = norm_eps;
+  ln.out = normed_out;
+  ln.stats = norm_stats;
+  return forward_impl(src_ptrs, src_row_stride, src_feat_stride, S, N, D, R, query, query_stride,
+                      eps, scale, out, out_row_stride, out_residual, logits, stats, ln, flags,
+                      stream);
 }
 
 extern "C" int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t D, int32_t R,

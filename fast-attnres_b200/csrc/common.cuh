@@ -47,6 +47,15 @@ struct FwdParams {
   __nv_bfloat16* out_residual;
   float* logits;  // [S,N]
   float* stats;   // [2,N]: max, 1/denominator
+  // Optional fused epilogue: LayerNorm over the D features of the BF16-rounded output row,
+  // ln_out = (out - mean) * rstd * ln_weight + ln_bias, written as BF16 [N,D] (contiguous)
+  // together with (mean, rstd) per row.  NULL `ln_out` disables it; NULL weight / bias mean
+  // ones / zeros.
+  const float* ln_weight;  // [D]
+  const float* ln_bias;    // [D]
+  float ln_eps;
+  __nv_bfloat16* ln_out;
+  float* ln_stats;  // [2,N]: mean, 1/sqrt(var + ln_eps)
 };
 
 struct BwdParams {

@@ -355,19 +355,103 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     __nv_bfloat16* orow = p.out + row * p.out_row_stride;
     __nv_bfloat16* rrow = p.out_residual != nullptr ? p.out_residual + row * (int64_t)D : nullptr;
     const float2 i2 = make_float2(inv_sum, inv_sum);
+    uint32_t hi[NV][4];  // the lane's share of the BF16 output row
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if (in_row[j]) {
-        uint32_t hi[4], lo[4];
+        uint32_t lo[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 o = __fmul2_rn(acc[j][k], i2);
-          hi[k] = pack_bf16x2(o.x, o.y);
-          lo[k] = split_low16x2(o.x, o.y, hi[k]);  // what the BF16 rounding dropped
+          hi[j][k] = pack_bf16x2(o.x, o.y);
+          lo[k] = split_low16x2(o.x, o.y, hi[j][k]);  // what the BF16 rounding dropped
         }
-        *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(orow + (int64_t)(gl + j * L) * 8) =
+            make_uint4(hi[j][0], hi[j][1], hi[j][2], hi[j][3]);
         if (rrow != nullptr)
           *reinterpret_cast<uint4*>(rrow + (int64_t)(gl + j * L) * 8) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) hi[j][k] = 0u;
+      }
+    }
+
+    // Fused LayerNorm of the row just written (from its BF16 values, so the result equals a
+    // LayerNorm applied to `out` afterwards): two more reductions over the group, then the
+    // normalised row goes out next to the plain one.
+    if (p.ln_out != nullptr) {
+      // Sum over the group of one value per lane; every lane gets the total.
+      auto group_total = [&](float value) {
+        value = warp_sum(value);
+        if (G > 1) {
+          float* mine = reinterpret_cast<float*>(part_sm + buf * kRingMaxGroupWarps);
+          if (lane == 0) mine[wig * 4] = value;
+          group_sync(group, L);
+          value = 0.f;
+#pragma unroll
+          for (int w = 0; w < G; ++w) value += mine[w * 4];
+          buf ^= 1;
+        }
+        return value;
+      };
+      const float inv_width = 1.0f / (float)D;
+      float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          sum2 = __fadd2_rn(sum2, make_float2(bf16x2_lo(hi[j][k]), bf16x2_hi(hi[j][k])));
+      const float mean = group_total(sum2.x + sum2.y) * inv_width;
+      const float2 nmean2 = make_float2(-mean, -mean);
+      float2 sq2 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (in_row[j]) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 d = __fadd2_rn(make_float2(bf16x2_lo(hi[j][k]), bf16x2_hi(hi[j][k])), nmean2);
+            sq2 = __ffma2_rn(d, d, sq2);
+          }
+        }
+      }
+      const float rstd = rsqrtf(group_total(sq2.x + sq2.y) * inv_width + p.ln_eps);
+      if (leader) {
+        p.ln_stats[row] = mean;
+        p.ln_stats[p.N + row] = rstd;
+      }
+      __nv_bfloat16* nrow = p.ln_out + row * (int64_t)D;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (in_row[j]) {
+          const int64_t first = (int64_t)(gl + j * L) * 8;
+          float w[8], b[8];
+          if (p.ln_weight != nullptr) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.ln_weight + first));
+            const float4 w1 = __ldg(reinterpret_cast<const float4*>(p.ln_weight + first) + 1);
+            w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
+            w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w[e] = 1.f;
+          }
+          if (p.ln_bias != nullptr) {
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.ln_bias + first));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.ln_bias + first) + 1);
+            b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
+            b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) b[e] = 0.f;
+          }
+          uint32_t y[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float x0 = (bf16x2_lo(hi[j][k]) - mean) * rstd;
+            const float x1 = (bf16x2_hi(hi[j][k]) - mean) * rstd;
+            y[k] = pack_bf16x2(fmaf(x0, w[2 * k], b[2 * k]), fmaf(x1, w[2 * k + 1], b[2 * k + 1]));
+          }
+          *reinterpret_cast<uint4*>(nrow + first) = make_uint4(y[0], y[1], y[2], y[3]);
+        }
       }
     }
   }

@@ -166,6 +166,46 @@ fwd_generic_kernel(const __grid_constant__ FwdParams p) {
           orow[d] = hi;
           if (rrow != nullptr)
             reinterpret_cast<unsigned short*>(rrow)[d] = split_low16(o, __bfloat16_as_ushort(hi));
+          acc[j * VEC + e] = __bfloat162float(hi);  // kept for the fused LayerNorm below
+        } else {
+          acc[j * VEC + e] = 0.f;
+        }
+      }
+    }
+    // Fused LayerNorm of the BF16 row just written (see FwdParams::ln_out).
+    if (p.ln_out != nullptr) {
+      float total[1] = {0.f};
+#pragma unroll
+      for (int i = 0; i < NE; ++i) total[0] += acc[i];
+      block_sum<1, T>(total, scratch, parity, tid);
+      const float mean = total[0] / (float)D;
+      total[0] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const int d = (j * T + tid) * VEC + e;
+          const float c = acc[j * VEC + e] - mean;
+          if (d < D) total[0] = fmaf(c, c, total[0]);
+        }
+      }
+      block_sum<1, T>(total, scratch, parity, tid);
+      const float rstd = rsqrtf(total[0] / (float)D + p.ln_eps);
+      if (tid == 0) {
+        p.ln_stats[row] = mean;
+        p.ln_stats[p.N + row] = rstd;
+      }
+      __nv_bfloat16* nrow = p.ln_out + row * (int64_t)D;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const int d = (j * T + tid) * VEC + e;
+          if (d < D) {
+            const float w = p.ln_weight != nullptr ? p.ln_weight[d] : 1.f;
+            const float b = p.ln_bias != nullptr ? p.ln_bias[d] : 0.f;
+            nrow[d] = __float2bfloat16_rn(fmaf((acc[j * VEC + e] - mean) * rstd, w, b));
+          }
         }
       }
     }

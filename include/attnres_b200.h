@@ -124,6 +124,37 @@ int attnres_b200_forward(
     uint32_t flags, void* stream);
 
 /*
+ * Forward read with the consumer's LayerNorm computed in the epilogue.  In the reference's
+ * model every read is followed by a LayerNorm of its result before the sublayer consumes it
+ * (benchmarks/model.py:156, 170 of the reference); the reference has no fused form, its
+ * LayerNorm re-reads `out` from memory.  Here the row is normalised while it is still in
+ * registers.  Everything attnres_b200_forward writes is written unchanged; in addition
+ *
+ *   normed_out   device BF16 [N,D] contiguous:
+ *                  (out - mean) * rstd * norm_weight + norm_bias
+ *                over the D features of the BF16-rounded `out` row (so the result equals a
+ *                LayerNorm applied to `out` afterwards, computed in FP32)
+ *   norm_stats   device FP32 [2,N] contiguous: mean, then rstd = 1/sqrt(var + norm_eps)
+ *                (biased variance), what a LayerNorm backward needs
+ *   norm_weight, device FP32 [D] contiguous; NULL means ones / zeros
+ *   norm_bias
+ *
+ * The backward of the pair is the LayerNorm backward (from `out`, `norm_stats` and the
+ * gradient of `normed_out`) followed by attnres_b200_backward.
+ */
+int attnres_b200_forward_layer_norm(
+    const void* const* src_ptrs, const int64_t* src_row_stride,
+    const int64_t* src_feat_stride,
+    int32_t S, int64_t N, int32_t D, int32_t R,
+    const void* query, int64_t query_stride,
+    float eps, float scale,
+    void* out, int64_t out_row_stride, void* out_residual,
+    float* logits, float* stats,
+    const float* norm_weight, const float* norm_bias, float norm_eps,
+    void* normed_out, float* norm_stats,
+    uint32_t flags, void* stream);
+
+/*
  * 1 when the backward of this shape (aligned layout assumed) is faster with the forward's
  * output and residual (it then finishes every source in one pass instead of staging the
  * whole position in shared memory), 0 otherwise.  Pure host function; plays the role of the

@@ -156,3 +156,51 @@ def test_accumulate_reads_strided_sources_and_stays_inside_its_buffers(shape):
     for i in range(s + 1):
         band = whole[i * (n * d + pad): i * (n * d + pad) + pad]
         assert bool((band == -3.0).all()), f"band {i} was written"
+
+
+def test_accumulating_and_sharded_reads_trace_under_torch_compile():
+    """Both extensions are torch.library operators (the accumulating backward declares its
+    buffers as mutated arguments): one full graph, no graph break, same bits as eager."""
+    from attnres.accumulate import attnres_accumulate
+    from attnres.parallel import sharded_attnres
+    torch.manual_seed(9)
+    s, n, d = 6, 300, 1024
+    sources = [torch.randn(n, d, device="cuda", dtype=BF16) for _ in range(s)]
+    upstream = torch.randn(n, d, device="cuda", dtype=BF16)
+
+    def accumulate_step(query, buffers):
+        out = attnres_accumulate(sources, query, buffers)
+        return (out.float() * upstream.float()).sum()
+
+    def sharded_step(query, leaves):
+        out = sharded_attnres(leaves, query)        # no process group: the local read
+        return (out.float() * upstream.float()).sum()
+
+    query = (torch.randn(d, device="cuda", dtype=BF16) * 0.1).requires_grad_()
+    eager_buffers = [torch.ones(n, d, device="cuda", dtype=BF16) for _ in range(s)]
+    accumulate_step(query, eager_buffers).backward()
+    eager_dq = query.grad.clone()
+
+    before = torch._dynamo.utils.counters["stats"]["unique_graphs"]
+    query2 = query.detach().clone().requires_grad_()
+    compiled_buffers = [torch.ones(n, d, device="cuda", dtype=BF16) for _ in range(s)]
+    torch.compile(accumulate_step, fullgraph=True, dynamic=False)(query2, compiled_buffers).backward()
+    assert torch.equal(query2.grad, eager_dq)
+    for a, e in zip(compiled_buffers, eager_buffers):
+        assert torch.equal(a, e)
+    assert torch._dynamo.utils.counters["stats"]["unique_graphs"] - before == 1
+
+    leaves = [t.clone().requires_grad_() for t in sources]
+    query3 = query.detach().clone().requires_grad_()
+    sharded_step(query3, leaves).backward()
+    leaves2 = [t.clone().requires_grad_() for t in sources]
+    query4 = query.detach().clone().requires_grad_()
+    torch.compile(sharded_step, fullgraph=True, dynamic=False)(query4, leaves2).backward()
+    assert torch.equal(query4.grad, query3.grad)
+    for a, e in zip(leaves2, leaves):
+        assert torch.equal(a.grad, e.grad)
+    # with a single rank the sharded read is the plain read
+    from attnres import attnres
+    query5 = query.detach().clone().requires_grad_()
+    (attnres(sources, query5).float() * upstream.float()).sum().backward()
+    assert torch.equal(query5.grad, query3.grad)

@@ -229,3 +229,19 @@ def test_info_command_keeps_the_reference_keys_and_runs_without_a_gpu():
             for text in ("fast-attnres 2.0.1", "torch:", "cuda available:", "triton available:",
                          "attnres API: CUDA BF16 only", "library state: ABI 3"):
                 assert text in done.stdout
+
+
+def test_fused_layer_norm_validates_like_attnres_on_cpu():
+    """`attnres_layer_norm` runs the reference's argument checks first and then insists on
+    CUDA tensors (nothing is launched on CPU)."""
+    from attnres.fused import attnres_layer_norm
+    values = torch.zeros(3, 4, 16, dtype=torch.bfloat16)
+    query = torch.zeros(8, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attnres_layer_norm(values, query)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attnres_layer_norm(list(values.unbind(0)), query, torch.ones(16), torch.zeros(16))
+    with pytest.raises(TypeError):
+        attnres_layer_norm(values.float(), query)
+    with pytest.raises(ValueError):
+        attnres_layer_norm(values, query, eps=0.0)
