@@ -32,7 +32,6 @@ from ._sources import DEFAULT_EPS, check_packed, check_sources
 def _check_buffers(buffers, shapes, device) -> None:
     if len(buffers) != len(shapes):
         raise ValueError("one gradient buffer per source is required")
-    spans = []
     for buffer, shape in zip(buffers, shapes):
         if not isinstance(buffer, torch.Tensor):
             raise TypeError("gradient buffers must be tensors")
@@ -46,10 +45,14 @@ def _check_buffers(buffers, shapes, device) -> None:
             raise ValueError("gradient buffers must be contiguous")
         if buffer.requires_grad:
             raise ValueError("gradient buffers must not require grad")
-        spans.append((buffer.data_ptr(), buffer.data_ptr() + buffer.numel() * buffer.element_size()))
-    # The kernels fetch a buffer row before they add to it: two sources whose buffers share
-    # any memory (the same tensor, or overlapping views of one storage) would lose an update.
-    spans.sort()
+    if not torch.compiler.is_compiling():   # addresses exist at run time only: the forward
+        _check_no_overlap(buffers)           # operator repeats this check when it runs
+
+
+def _check_no_overlap(buffers) -> None:
+    """The kernels fetch a buffer row before they add to it: two sources whose buffers share
+    any memory (the same tensor, or overlapping views of one storage) would lose an update."""
+    spans = sorted((b.data_ptr(), b.data_ptr() + b.numel() * b.element_size()) for b in buffers)
     for (_, end), (start, _) in zip(spans, spans[1:]):
         if start < end:
             raise ValueError("every source needs its own gradient buffer (buffers overlap)")
@@ -68,6 +71,7 @@ def accumulate_sources_forward(sources: list[torch.Tensor], query: torch.Tensor,
                                overwrite: bool
                                ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     _ops._require_cuda_bf16(sources, query)
+    _check_no_overlap(buffers)
     kept, ptrs, rs, fs = _ops._source_table(sources)
     return _ops._run_forward(kept, ptrs, rs, fs, sources[0].shape, query, eps, scale,
                              keep_residual=True)

@@ -119,10 +119,11 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
   return launch_bwd_generic<1, 32, 256, 2>(p, grid, st);
 }
 
-// Rows of the dquery workspace per SM: one per resident position stream.  (Twelve rows for
-// D <= 1024, where four one-warp groups per CTA would allow three CTAs per SM instead of two,
-// measured no faster.)
-constexpr int kWorkspaceRowsPerSm = 8;
+// Rows of the dquery workspace per SM: one per resident position stream.  Rows of up to 1024
+// features are owned by one-warp groups, four to a CTA; twelve rows let the one-pass backward
+// keep three CTAs per SM instead of two there (S = 49, D = 1024: 5.11 -> 5.55 TB/s; the staged
+// and register-resident kernels run fewer streams and do not change).
+inline int workspace_rows_per_sm(int D) { return D <= 1024 ? 12 : 8; }
 
 // The one-pass backward moves 6*D more bytes per position (the forward writes one more BF16
 // row, which costs it 1/(S+1) of its time; the backward reads two more) and finishes each
@@ -385,7 +386,7 @@ extern "C" int32_t attnres_b200_dq_workspace_rows(int64_t N, int32_t S, int32_t 
   if (int st = check_shape(S, N, D, R)) return -st;
   int sms = 0;
   if (int st = sm_count(device, &sms)) return -st;
-  const int64_t cap = (int64_t)sms * kWorkspaceRowsPerSm;
+  const int64_t cap = (int64_t)sms * workspace_rows_per_sm(D);
   return (int32_t)(N < cap ? N : cap);
 }
 
@@ -450,7 +451,7 @@ extern "C" int attnres_b200_backward(
   int device = 0, sms = 0;
   if (int st = current_device(&device)) return st;
   if (int st = sm_count(device, &sms)) return st;
-  const int64_t cap = (int64_t)sms * kWorkspaceRowsPerSm;
+  const int64_t cap = (int64_t)sms * workspace_rows_per_sm(D);
   const int max_rows = (int)(N < cap ? N : cap);
   if (want_dq && dq_partial_rows < max_rows) return ATTNRES_B200_ERR_WORKSPACE;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);

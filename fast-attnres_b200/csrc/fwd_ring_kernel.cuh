@@ -146,7 +146,7 @@ __device__ __forceinline__ void mbar_wait_fast(uint64_t* bar, uint32_t parity,
   if (!mbar_try_wait(bar, parity)) mbar_wait_slow(bar, parity, abort_flag);
 }
 
-template <int G, int TAIL0, bool SR>
+template <int G, int TAIL0, bool SR, bool LN>
 __global__ void __launch_bounds__((G > 4 ? 8 : 4) * 32, G > 4 ? 1 : 3)
 fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ FwdRingPlan plan) {
   constexpr int NV = kRingChunks, B = kRingBatch;
@@ -379,7 +379,7 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     // Fused LayerNorm of the row just written (from its BF16 values, so the result equals a
     // LayerNorm applied to `out` afterwards): two more reductions over the group, then the
     // normalised row goes out next to the plain one.
-    if (p.ln_out != nullptr) {
+    if constexpr (LN) {
       // Sum over the group of one value per lane; every lane gets the total.
       auto group_total = [&](float value) {
         value = warp_sum(value);
@@ -464,17 +464,34 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
   }
 }
 
-// Compile-time ring constants measured 1 % faster for eight-warp groups (D = 8192) and 1 to
-// 7 % slower for the narrower ones (D = 4096: 5.9 against 6.4 TB/s at S = 49), so only the
-// eight-warp instances use them.
-template <int G, int TAIL0>
-inline int launch_fwd_ring(const FwdParams& p, const FwdRingPlan& plan, int grid,
-                           cudaStream_t stream) {
-  auto kernel = fwd_ring_kernel<G, TAIL0, (G == 8 && TAIL0 >= 0)>;
+// Compile-time ring constants (SR), measured on B200 at N = 16384, R = D: eight-warp groups
+// +1 %; one-warp groups +4 % at S = 49 and even at S = 9; two-warp groups +6 % at S = 49 but
+// -3 % at S = 9; four-warp groups -5 % (D = 4096, S = 49: 6.07 against 6.37 TB/s).  So they are
+// used for one- and eight-warp groups, and for two-warp groups from 17 sources up.  The
+// instances with the LayerNorm epilogue (LN) are separate so that the plain forward carries
+// none of its registers; they use the run-time ring form except for eight-warp groups.
+template <int G, int TAIL0, bool SR, bool LN>
+inline int launch_fwd_ring_instance(const FwdParams& p, const FwdRingPlan& plan, int grid,
+                                    cudaStream_t stream) {
+  auto kernel = fwd_ring_kernel<G, TAIL0, SR, LN>;
   static SmemGrant grant;
   if (int st = prepare_kernel(kernel, plan.smem_bytes, grant)) return st;
   kernel<<<grid, plan.cta_warps * 32, plan.smem_bytes, stream>>>(p, plan);
   return cudaGetLastError() == cudaSuccess ? 0 : 9;
+}
+
+template <int G, int TAIL0>
+inline int launch_fwd_ring(const FwdParams& p, const FwdRingPlan& plan, int grid,
+                           cudaStream_t stream) {
+  constexpr bool kFull = TAIL0 >= 0;  // full rows always have the eight-stage ring
+  if (p.ln_out != nullptr)
+    return launch_fwd_ring_instance<G, TAIL0, (G == 8 && kFull), true>(p, plan, grid, stream);
+  if constexpr (kFull && (G == 1 || G == 8))
+    return launch_fwd_ring_instance<G, TAIL0, true, false>(p, plan, grid, stream);
+  if constexpr (kFull && G == 2) {
+    if (p.S >= 17) return launch_fwd_ring_instance<G, TAIL0, true, false>(p, plan, grid, stream);
+  }
+  return launch_fwd_ring_instance<G, TAIL0, false, false>(p, plan, grid, stream);
 }
 
 template <int G>

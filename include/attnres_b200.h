@@ -255,7 +255,7 @@ const char* attnres_b200_kernel_family(int32_t S, int32_t D, int32_t R, int32_t 
  *     to be cleared.  Two calls that overlap on the GPU (different streams, or
  *     graphs replayed concurrently) race on the array: serialise them.
  */
-#define ATTNRES_B200_STATIC_SCRATCH_FLOATS 2424832 /* 1184 rows x 2048 */
+#define ATTNRES_B200_STATIC_SCRATCH_FLOATS 2424832 /* 148 SMs: 1184 rows x 2048, 1776 rows x 1024 */
 int attnres_b200_backward_static_scratch(
     const void* const* src_ptrs, const int64_t* src_row_stride,
     const int64_t* src_feat_stride,
