@@ -199,9 +199,9 @@ class CausalLM(nn.Module):
         return self.lm_head(self.read(schedule.sources(), config.events - 1))
 
 
-def make_optimizer(model, *, capturable: bool):
+def make_optimizer(model, *, capturable: bool, lr: float = 3e-4):
     """The reference's optimiser settings (benchmarks/run.py:2369-2375 of the reference)."""
-    return torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
+    return torch.optim.AdamW(model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1,
                              fused=True, capturable=capturable)
 
 

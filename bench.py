@@ -709,7 +709,11 @@ def run_model_workload(args, rank: int, world: int, local_rank: int) -> None:
         wrapped = torch.nn.parallel.DistributedDataParallel(
             model, device_ids=[local_rank], gradient_as_bucket_view=True, bucket_cap_mb=256)
     runner = torch.compile(wrapped, fullgraph=False) if args.compile else wrapped
-    optimizer = lm.make_optimizer(model, capturable=False)
+    # The reference's learning rate (3e-4) is set for its 1024-wide models; Adam's first steps
+    # move every weight by the learning rate, which at 4096 features per row sends the loss up,
+    # so wider models take it scaled by 1024 / width.
+    learning_rate = 3e-4 * min(1.0, 1024 / config.width)
+    optimizer = lm.make_optimizer(model, capturable=False, lr=learning_rate)
     generator = torch.Generator(device=device).manual_seed(SEED + 1 + rank)
     shape = (batch_per_gpu * accumulation, config.sequence)
     tokens = torch.randint(config.vocab, shape, device=device, generator=generator)
@@ -774,7 +778,7 @@ def run_model_workload(args, rank: int, world: int, local_rank: int) -> None:
                    "microbatches_per_gpu_step": accumulation,
                    "global_batch_sequences": batch_per_gpu * accumulation * world,
                    "parameters": parameters, "parameter_count": parameters_count,
-                   "optimizer": "AdamW fused lr 3e-4 betas 0.9/0.95 wd 0.1",
+                   "optimizer": f"AdamW fused lr {learning_rate:g} betas 0.9/0.95 wd 0.1",
                    "compiled": bool(args.compile),
                    "parallelism": f"data parallel x{world} (DistributedDataParallel, NCCL, "
                                   "256 MB buckets overlapping the backward)",

@@ -125,7 +125,7 @@ int dispatch_bwd_generic(const BwdParams& p, bool vec, int grid, cudaStream_t st
 // and register-resident kernels run fewer streams and do not change).
 inline int workspace_rows_per_sm(int D) { return D <= 1024 ? 12 : 8; }
 
-// The one-pass backward moves 6*D more bytes per position (the forward writes one more BF16
+// The one-pass backward moves 6*D more bytes per position (the forward writes one more 16-bit
 // row, which costs it 1/(S+1) of its time; the backward reads two more) and finishes each
 // source as it arrives.  Measured on B200 against the two-pass kernels, forward and backward
 // together (N = 16384, R = D unless noted):
@@ -134,11 +134,14 @@ inline int workspace_rows_per_sm(int D) { return D <= 1024 ? 12 : 8; }
 //     rows take more than half an SM's shared memory (S >= 33 at D = 2048, S >= 65 at
 //     D = 1024): 1.4x to 5x on the backward;
 //   * full-width rows with R = D: at D >= 4096 it wins from S = 5 up (backward 5.3 vs 3.9 TB/s
-//     at S = 5, 6.3 vs 6.0 at S = 25); at D = 2048 it wins for S = 5..9 (4.7 vs 3.9, 5.2 vs
-//     4.8) and loses the forward's extra row again at S = 17 and 25 (backward within 1 %);
+//     at S = 5, 6.3 vs 6.0 at S = 25); at D = 2048 it wins from S = 5 up as well (S = 13:
+//     494 vs 524 us, S = 17: 619 vs 645 us, S = 25: 870 vs 887 us for forward + backward);
+//   * D = 1024 (one-warp groups, three CTAs per SM): it wins where the staged backward keeps
+//     three CTAs or fewer per SM (S = 33: 629 vs 662 us, S = 49: 885 vs 1055 us) and up to
+//     twelve sources (S = 5: 137 vs 150 us, S = 9: 209 vs 219 us; S = 13 ties); S = 17 and 25
+//     stay with the staged kernel by 2 %; narrower rows (D = 512) stay with it by 20 to 30 %;
 //   * up to four sources: the register-resident kernel wins (S = 2, 3: 5.7 vs 4.3 TB/s) or
 //     ties once the forward's extra row is counted (S = 4, D = 4096: 388 vs 386 us);
-//   * D <= 1024: it wins only once the staged backward is down to two CTAs per SM (S = 49);
 //   * low-rank tails at D = 4096 with a staged backward that fits one SM (S = 16, R = 1024:
 //     5.45 vs 5.31 TB/s) and short low-rank lists: the two-pass kernels stay ahead by 3 to 6 %.
 bool wants_output_residual(int S, int D, int R) {
@@ -153,8 +156,8 @@ bool wants_output_residual(int S, int D, int R) {
   const bool one_position_per_sm = (size_t)(S + 1) * (size_t)D * 2u > 114u * 1024u;
   if (D <= 2048 && one_position_per_sm) return true;
   const bool full_row = D / 8 == stream.group_warps * 32 * kRingChunks;
-  if (full_row && R == D && (D >= 4096 || (D >= 2048 && S <= 12))) return true;
-  return D <= 1024 && stash.ctas_per_sm <= 2;
+  if (full_row && R == D && D >= 2048) return true;
+  return D <= 1024 && (stash.ctas_per_sm <= 3 || (full_row && R == D && S <= 12));
 }
 
 // Everything about a backward call that can be judged without touching the device or the

@@ -118,11 +118,17 @@ def test_selftest_entry_point_checks_its_arguments():
 
 def test_output_residual_policy_is_a_pure_host_decision():
     # lists of up to four sources never want it; a position that fills an SM's shared
-    # memory does, and so do full-width rows of 2048 and more with a full-rank query
+    # memory does, and so do full-width rows of 2048 and more with a full-rank query from five
+    # sources up; at 1024 features the middle source counts stay with the staged kernel
     assert not _native.wants_output_residual(2, 1024, 1024)
     assert not _native.wants_output_residual(4, 4096, 4096)
     assert not _native.wants_output_residual(25, 1024, 1024)
-    assert not _native.wants_output_residual(25, 2048, 2048)
+    assert not _native.wants_output_residual(17, 1024, 1024)
+    assert _native.wants_output_residual(5, 1024, 1024)
+    assert not _native.wants_output_residual(5, 512, 512)
+    assert _native.wants_output_residual(25, 2048, 2048)
+    assert _native.wants_output_residual(9, 1024, 1024)
+    assert _native.wants_output_residual(33, 1024, 1024)
     assert not _native.wants_output_residual(7, 4096, 1024)
     assert not _native.wants_output_residual(16, 4096, 1024)
     assert _native.wants_output_residual(25, 4096, 4096)
