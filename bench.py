@@ -14,7 +14,13 @@ from L2 between timed passes.
 With N > 1 (torchrun) every rank owns its own 16 384 positions of every cell
 (position sharding, no data-path collective; weak scaling) and the FP32 query
 gradients of all cells are summed over NCCL (one bucketed all-reduce per step) before the
-BF16 cast.
+BF16 cast.  The same line then carries a `strong` record (the 16 384 positions of every
+cell split over the ranks), every rank's own kernel time and the collective's own time.
+
+`--workload config4|config5` times a training step of the benchmark language model instead
+(baseline/lm.py: the reference's 24-layer Full-schedule and 8-GPU Block-schedule
+configurations), data-parallel over the ranks with the gradient all-reduce overlapping the
+backward.
 
 Printed JSON (rank 0, one line): whole-job tokens/s (`value`), the HBM roofline
 of the dominant (backward) kernel, the same metric end to end from pinned host
