@@ -12,8 +12,8 @@ such form; this module is new.
 The normalisation is taken over the BF16-rounded read (what a separate LayerNorm would see) in
 FP32.  It is a ``torch.library`` operator with a fake kernel and registered autograd, so it
 traces under ``torch.compile(fullgraph=True)`` and captures into CUDA graphs; its backward is
-the LayerNorm backward (plain tensor operations, which Inductor fuses) followed by the read's
-backward operator.
+two operators, the LayerNorm backward (from the saved read and the saved mean / rstd) and the
+read's backward.
 """
 from __future__ import annotations
 
@@ -71,6 +71,30 @@ def _(sources, query, weight, bias, eps, scale, norm_eps):
             first.new_empty(first.shape if keep else (0,), dtype=torch.int16))
 
 
+@_ops._custom_op("attnres_b200::layer_norm_backward", mutates_args=(), device_types="cuda")
+def layer_norm_backward(grad_normed: torch.Tensor, out: torch.Tensor, norm_stats: torch.Tensor,
+                        weight: torch.Tensor
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of the fused LayerNorm from what the forward saved: the BF16 read `out` and
+    (mean, rstd) per row.  -> (gradient of `out` in BF16, weight gradient, bias gradient in
+    FP32).  One opaque operator, so a compiled training step sees two operators per read in
+    its backward (this one and the read's backward) instead of a dozen tensor operations."""
+    width = out.shape[-1]
+    rows = norm_stats.shape[1]
+    mean = norm_stats[0].reshape(rows, 1)
+    rstd = norm_stats[1].reshape(rows, 1)
+    through, grad_weight, grad_bias = torch.ops.aten.native_layer_norm_backward(
+        grad_normed.reshape(rows, width).float(), out.reshape(rows, width).float(), [width], mean,
+        rstd, weight, None, [True, True, True])
+    return through.to(torch.bfloat16).reshape(out.shape), grad_weight, grad_bias
+
+
+@layer_norm_backward.register_fake
+def _(grad_normed, out, norm_stats, weight):
+    return (out.new_empty(out.shape), weight.new_empty(weight.shape),
+            weight.new_empty(weight.shape))
+
+
 def _setup(ctx, inputs, output) -> None:
     sources, query, weight, bias, eps, scale, norm_eps = inputs
     normed, out, norm_stats, logits, stats, residual = output
@@ -90,21 +114,12 @@ def _backward(ctx, grad_normed, grad_out, *_unused):
     saved = ctx.saved_tensors
     sources, query, weight, norm_stats, logits, stats, out, residual = (
         list(saved[:count]), *saved[count:])
-    width = out.shape[-1]
     grad_weight = grad_bias = None
-    total = None if grad_out is None else grad_out.float()
+    total = grad_out
     if grad_normed is not None:
-        lead = out.shape[:-1]
-        mean = norm_stats[0].reshape(*lead, 1)
-        rstd = norm_stats[1].reshape(*lead, 1)
-        g = grad_normed.float()
-        xhat = (out.float() - mean) * rstd
-        gw = g * weight
-        through = rstd * (gw - gw.mean(-1, keepdim=True) - xhat * (gw * xhat).mean(-1, keepdim=True))
-        total = through if total is None else total + through
-        grad_weight = (g * xhat).reshape(-1, width).sum(0)
-        grad_bias = g.reshape(-1, width).sum(0)
-    gradients = _ops.read_sources_backward(sources, query, total.to(torch.bfloat16), logits, stats,
+        through, grad_weight, grad_bias = layer_norm_backward(grad_normed, out, norm_stats, weight)
+        total = through if total is None else (total.float() + through.float()).to(torch.bfloat16)
+    gradients = _ops.read_sources_backward(sources, query, total, logits, stats,
                                            out, residual, float(ctx.eps), float(ctx.scale), False)
     return gradients[:count], gradients[count], grad_weight, grad_bias, None, None, None
 

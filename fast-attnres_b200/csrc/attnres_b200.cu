@@ -77,7 +77,8 @@ int fill_sources(SourceTable& t, const void* const* ptrs, const int64_t* rs, con
 
 template <int VEC, int NJ, int T, int B>
 int launch_fwd_generic(const FwdParams& p, int grid, cudaStream_t stream) {
-  fwd_generic_kernel<VEC, NJ, T, B><<<grid, T, 0, stream>>>(p);
+  if (p.ln_out != nullptr) fwd_generic_kernel<VEC, NJ, T, B, true><<<grid, T, 0, stream>>>(p);
+  else fwd_generic_kernel<VEC, NJ, T, B, false><<<grid, T, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
 }
 

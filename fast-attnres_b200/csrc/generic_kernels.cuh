@@ -59,7 +59,9 @@ __device__ __forceinline__ void block_sum(float* vals, float* scratch, int& pari
   parity ^= 1;
 }
 
-template <int VEC, int NJ, int T, int B>
+// LN: also write the LayerNorm of the row (FwdParams::ln_out); a separate instance so that
+// the plain forward carries none of it.
+template <int VEC, int NJ, int T, int B, bool LN>
 __global__ void __launch_bounds__(T)
 fwd_generic_kernel(const __grid_constant__ FwdParams p) {
   constexpr int NE = VEC * NJ;
@@ -166,14 +168,14 @@ fwd_generic_kernel(const __grid_constant__ FwdParams p) {
           orow[d] = hi;
           if (rrow != nullptr)
             reinterpret_cast<unsigned short*>(rrow)[d] = split_low16(o, __bfloat16_as_ushort(hi));
-          acc[j * VEC + e] = __bfloat162float(hi);  // kept for the fused LayerNorm below
-        } else {
+          if (LN) acc[j * VEC + e] = __bfloat162float(hi);  // kept for the LayerNorm below
+        } else if (LN) {
           acc[j * VEC + e] = 0.f;
         }
       }
     }
     // Fused LayerNorm of the BF16 row just written (see FwdParams::ln_out).
-    if (p.ln_out != nullptr) {
+    if constexpr (LN) {
       float total[1] = {0.f};
 #pragma unroll
       for (int i = 0; i < NE; ++i) total[0] += acc[i];
