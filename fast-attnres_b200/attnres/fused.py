@@ -85,7 +85,7 @@ def layer_norm_backward(grad_normed: torch.Tensor, out: torch.Tensor, norm_stats
     rstd = norm_stats[1].reshape(rows, 1)
     through, grad_weight, grad_bias = torch.ops.aten.native_layer_norm_backward(
         grad_normed.reshape(rows, width).float(), out.reshape(rows, width).float(), [width], mean,
-        rstd, weight, None, [True, True, True])
+        rstd, weight, weight, [True, True, True])   # the bias argument only lends its shape
     return through.to(torch.bfloat16).reshape(out.shape), grad_weight, grad_bias
 
 
