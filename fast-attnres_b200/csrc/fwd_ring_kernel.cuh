@@ -354,7 +354,9 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
     }
     __nv_bfloat16* orow = p.out + row * p.out_row_stride;
     __nv_bfloat16* rrow = p.out_residual != nullptr ? p.out_residual + row * (int64_t)D : nullptr;
-    const float2 i2 = make_float2(inv_sum, inv_sum);
+    // out = acc / run_sum: multiply by the reciprocal, then one Newton step on the quotient
+    // (o += (acc - o * sum) * inv), which removes the reciprocal's own rounding.
+    const float2 i2 = make_float2(inv_sum, inv_sum), nsum2 = make_float2(-run_sum, -run_sum);
     uint32_t hi[NV][4];  // the lane's share of the BF16 output row
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -362,7 +364,8 @@ fwd_ring_kernel(const __grid_constant__ FwdParams p, const __grid_constant__ Fwd
         uint32_t lo[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 o = __fmul2_rn(acc[j][k], i2);
+          const float2 first = __fmul2_rn(acc[j][k], i2);
+          const float2 o = __ffma2_rn(__ffma2_rn(first, nsum2, acc[j][k]), i2, first);
           hi[j][k] = pack_bf16x2(o.x, o.y);
           lo[k] = split_low16x2(o.x, o.y, hi[j][k]);  // what the BF16 rounding dropped
         }
