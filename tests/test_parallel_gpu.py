@@ -1,4 +1,5 @@
-"""Position sharding on real GPUs (needs two devices; skipped on a one-GPU box).
+"""Position sharding on real GPUs: two ranks on two devices over NCCL (skipped on a one-GPU box),
+and two ranks sharing ONE device over gloo, which runs everywhere.
 
 Each rank runs the CUDA kernels on its own rows; the FP32 query gradients meet in one NCCL
 all-reduce and are rounded to BF16 once.  The result must equal the unsharded read: outputs and
@@ -13,8 +14,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")]
+pytestmark = pytest.mark.gpu
+needs_two_gpus = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 
 
 def _free_port() -> int:
@@ -31,7 +32,7 @@ def _inputs(device):
     return values, query, upstream
 
 
-def _worker(rank, world, port, as_list, results):
+def _worker(rank, world, port, as_list, results, backend="nccl"):
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
@@ -40,11 +41,17 @@ def _worker(rank, world, port, as_list, results):
             sys.path.insert(0, str(entry))
     from attnres.parallel import shard_rows, sharded_attnres
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+    # NCCL wants one device per rank; over gloo (host-staged collectives, nothing in a kernel
+    # waits for another rank) both ranks may share device 0.
+    device_index = rank if backend == "nccl" else 0
+    torch.cuda.set_device(device_index)
+    if backend == "nccl":
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", device_index))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        values, query, upstream = _inputs(f"cuda:{rank}")
+        values, query, upstream = _inputs(f"cuda:{device_index}")
         start, stop = shard_rows(values.shape[1], world, rank)
         mine = values[:, start:stop].contiguous().requires_grad_()
         q = query.clone().requires_grad_()
@@ -59,13 +66,12 @@ def _worker(rank, world, port, as_list, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("as_list", [False, True], ids=["packed", "list"])
-def test_two_gpu_sharding_equals_the_unsharded_read(as_list):
+def _check_against_unsharded(backend, as_list):
     from attnres import attnres
     world, port = 2, _free_port()
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, port, as_list, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, as_list, results, backend), nprocs=world, join=True)
     values, query, upstream = _inputs("cuda:0")
     values.requires_grad_()
     query.requires_grad_()
@@ -79,3 +85,17 @@ def test_two_gpu_sharding_equals_the_unsharded_read(as_list):
         assert torch.equal(dv_r, dv[:, start:stop].cpu())
         assert torch.equal(dq_r, back(results[0][4])), "ranks disagree on the reduced query gradient"
         torch.testing.assert_close(dq_r.float(), dq.cpu().float(), rtol=2**-7, atol=2**-7)
+
+
+@needs_two_gpus
+@pytest.mark.parametrize("as_list", [False, True], ids=["packed", "list"])
+def test_two_gpu_sharding_equals_the_unsharded_read(as_list):
+    _check_against_unsharded("nccl", as_list)
+
+
+@pytest.mark.parametrize("as_list", [False, True], ids=["packed", "list"])
+def test_two_ranks_on_one_gpu_equal_the_unsharded_read(as_list):
+    """The same check with both ranks on device 0 and the FP32 query gradients summed over
+    gloo: runs on a one-GPU box, so the sharded read's kernels and its collective are covered
+    wherever the GPU tests run."""
+    _check_against_unsharded("gloo", as_list)
