@@ -570,7 +570,7 @@ def run_e2e(args, cells, device, distributed, world=1) -> dict:
     steps = max(1, min(args.steps, 3))
     max_elems = max(c.S * ROWS * c.D for c in cells)
     max_row = ROWS * max(WIDTHS)
-    block_rows = min(E2E_BLOCK_ROWS, ROWS)
+    block_rows = min(args.e2e_block_rows or E2E_BLOCK_ROWS, ROWS)
     block_elems = max(c.S * block_rows * c.D for c in cells)
     block_row = block_rows * max(WIDTHS)
     host_values = torch.empty(max_elems, dtype=torch.bfloat16).pin_memory()
@@ -923,6 +923,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--skip-e2e", action="store_true",
                         help="profiling runs: leave out the host-buffer end-to-end leg")
+    parser.add_argument("--e2e-block-rows", type=int, default=0,
+                        help="rows per host-to-device block of the end-to-end leg (default 4096)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="profiling runs: leave out the CPU-oracle leg")
     parser.add_argument("--workload", choices=("sweep", *MODEL_WORKLOADS), default="sweep",

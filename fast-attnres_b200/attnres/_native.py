@@ -39,6 +39,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_float, c_void_p, c_void_p,
         c_uint32, c_void_p]),
+    "attnres_b200_layer_norm_workspace_rows": (c_int32, [c_int64, c_int32, c_int32]),
+    "attnres_b200_layer_norm_backward": (c_int32, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
+        c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
     "attnres_b200_wants_output_residual": (c_int32, [c_int32, c_int32, c_int32]),
     "attnres_b200_backward_static_scratch": (c_int32, [
         _PTR_ARRAY, _I64_ARRAY, _I64_ARRAY,
@@ -122,6 +126,25 @@ def forward_layer_norm(src_ptrs, row_strides, feat_strides, S, N, D, R, query_pt
         out_ptr, out_row_stride, residual_ptr, logits_ptr, stats_ptr,
         weight_ptr, bias_ptr, norm_eps, normed_ptr, norm_stats_ptr, flags, stream)
     check(status, "attnres_b200_forward_layer_norm")
+
+
+ERR_MISALIGNED = 7
+
+
+def layer_norm_workspace_rows(N, D, device_index) -> int:
+    rows = load().attnres_b200_layer_norm_workspace_rows(N, D, device_index)
+    if rows < 0:
+        check(-rows, "attnres_b200_layer_norm_workspace_rows")
+    return rows
+
+
+def layer_norm_backward(grad_ptr, grad_row_stride, out_ptr, stats_ptr, weight_ptr, N, D,
+                        grad_out_ptr, partials_ptr, partial_rows, grad_weight_bias_ptr,
+                        stream) -> int:
+    """Returns the status code (0 = enqueued; ERR_MISALIGNED = layout outside the kernel's)."""
+    return load().attnres_b200_layer_norm_backward(
+        grad_ptr, grad_row_stride, out_ptr, stats_ptr, weight_ptr, N, D, grad_out_ptr,
+        partials_ptr, partial_rows, grad_weight_bias_ptr, stream)
 
 
 def wants_output_residual(S, D, R) -> bool:

@@ -77,10 +77,30 @@ def layer_norm_backward(grad_normed: torch.Tensor, out: torch.Tensor, norm_stats
                         ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Backward of the fused LayerNorm from what the forward saved: the BF16 read `out` and
     (mean, rstd) per row.  -> (gradient of `out` in BF16, weight gradient, bias gradient in
-    FP32).  One opaque operator, so a compiled training step sees two operators per read in
-    its backward (this one and the read's backward) instead of a dozen tensor operations."""
+    FP32), computed by the library's LayerNorm-backward kernel (6 D bytes per row: the gradient
+    and the read in, the input gradient out).  One opaque operator, so a compiled training
+    step sees two operators per read in its backward: this one and the read's backward."""
     width = out.shape[-1]
     rows = norm_stats.shape[1]
+    device = out.device
+    grad_rows = grad_normed.reshape(rows, width)
+    if grad_rows.stride(-1) != 1:
+        grad_rows = grad_rows.contiguous()
+    out_rows = out.reshape(rows, width).contiguous()
+    through = torch.empty((rows, width), device=device, dtype=torch.bfloat16)
+    both = torch.empty((2 * width,), device=device, dtype=torch.float32)
+    with torch.cuda.device(device):
+        partial_rows = _native.layer_norm_workspace_rows(rows, width, device.index)
+        partials = torch.empty((partial_rows, 2 * width), device=device, dtype=torch.float32)
+        status = _native.layer_norm_backward(
+            grad_rows.data_ptr(), int(grad_rows.stride(0)), out_rows.data_ptr(),
+            norm_stats.data_ptr(), weight.data_ptr(), rows, width, through.data_ptr(),
+            partials.data_ptr(), partial_rows, both.data_ptr(), _ops._stream(device))
+    if status == 0:
+        return through.reshape(out.shape), both[:width].clone(), both[width:].clone()
+    if status != _native.ERR_MISALIGNED:
+        _native.check(status, "attnres_b200_layer_norm_backward")
+    # A width or an alignment outside the kernel's: aten's LayerNorm backward on FP32 copies.
     mean = norm_stats[0].reshape(rows, 1)
     rstd = norm_stats[1].reshape(rows, 1)
     through, grad_weight, grad_bias = torch.ops.aten.native_layer_norm_backward(

@@ -568,3 +568,68 @@ extern "C" int attnres_b200_selftest_wait_limit(const void* scratch16, uint64_t 
   selftest_wait_limit_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(scratch16, limit_ns);
   return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward of the fused LayerNorm epilogue.
+
+namespace {
+constexpr int kLayerNormRowsPerSm = 8;
+
+template <int NJ, int T>
+int launch_layer_norm_bwd(const LayerNormBwdParams& p, int grid, cudaStream_t stream) {
+  layer_norm_bwd_kernel<NJ, T><<<grid, T, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
+}
+}  // namespace
+
+extern "C" int32_t attnres_b200_layer_norm_workspace_rows(int64_t N, int32_t D, int32_t device) {
+  if (D < 1 || D > kMaxWidth) return -ATTNRES_B200_ERR_BAD_WIDTH;
+  if (N < 1) return -ATTNRES_B200_ERR_BAD_ROWS;
+  int sms = 0;
+  if (int st = sm_count(device, &sms)) return -st;
+  const int64_t cap = (int64_t)sms * kLayerNormRowsPerSm;
+  return (int32_t)(N < cap ? N : cap);
+}
+
+extern "C" int attnres_b200_layer_norm_backward(
+    const void* grad_normed, int64_t grad_row_stride, const void* out, const float* norm_stats,
+    const float* norm_weight, int64_t N, int32_t D,
+    void* grad_out, float* partials, int32_t partial_rows, float* grad_weight_bias,
+    void* stream) {
+  if (D < 1 || D > kMaxWidth) return ATTNRES_B200_ERR_BAD_WIDTH;
+  if (N < 1) return ATTNRES_B200_ERR_BAD_ROWS;
+  if (!grad_normed || !out || !norm_stats || !grad_out || !partials || !grad_weight_bias)
+    return ATTNRES_B200_ERR_NULL_POINTER;
+  // 16-byte accesses along the rows; other layouts are the caller's to handle.
+  if (D % 8 != 0 || !aligned16(grad_normed) || !aligned16(out) || !aligned16(grad_out) ||
+      !aligned16(partials) || (N > 1 && grad_row_stride % 8 != 0))
+    return ATTNRES_B200_ERR_MISALIGNED;
+  int device = 0, sms = 0;
+  if (int st = current_device(&device)) return st;
+  if (int st = sm_count(device, &sms)) return st;
+  const int64_t cap = (int64_t)sms * kLayerNormRowsPerSm;
+  const int grid = (int)(N < cap ? N : cap);
+  if (partial_rows < grid) return ATTNRES_B200_ERR_WORKSPACE;
+  LayerNormBwdParams p;
+  p.grad = static_cast<const __nv_bfloat16*>(grad_normed);
+  p.grad_row_stride = grad_row_stride;
+  p.x = static_cast<const __nv_bfloat16*>(out);
+  p.stats = norm_stats;
+  p.weight = norm_weight;
+  p.dx = static_cast<__nv_bfloat16*>(grad_out);
+  p.partials = partials;
+  p.N = N;
+  p.D = D;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  int st;
+  if (D <= 1024) st = launch_layer_norm_bwd<1, 128>(p, grid, cs);
+  else if (D <= 2048) st = launch_layer_norm_bwd<1, 256>(p, grid, cs);
+  else if (D <= 4096) st = launch_layer_norm_bwd<2, 256>(p, grid, cs);
+  else st = launch_layer_norm_bwd<4, 256>(p, grid, cs);
+  if (st != ATTNRES_B200_OK) return st;
+  const int columns = 2 * D;
+  dq_reduce_kernel<<<(columns + kDqReduceColumns - 1) / kDqReduceColumns,
+                     kDqReduceColumns * kDqReduceGroups, 0, cs>>>(partials, grid, columns, nullptr,
+                                                                  grad_weight_bias);
+  return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
+}

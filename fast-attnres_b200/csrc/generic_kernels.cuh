@@ -377,6 +377,97 @@ bwd_generic_kernel(const __grid_constant__ BwdParams p) {
   }
 }
 
+// Backward of the LayerNorm that the fused forward epilogue applies (FwdParams::ln_out), from
+// what that forward saved: the BF16 row x (`out`) and (mean, rstd) per row.
+//   xhat = (x - mean) * rstd,  gw = g * w,
+//   dx   = rstd * (gw - mean_d(gw) - xhat * mean_d(gw * xhat))          -> BF16 [N,D]
+//   dw  += g * xhat,  db += g                                            -> per-CTA FP32 partials
+// One CTA walks rows; a thread owns the same NJ chunks of eight columns in every row, so its
+// weights and its weight / bias gradient sums stay in registers for the whole launch.  The
+// partial rows ([gridDim.x, 2 D]: weight gradient, then bias gradient) are summed by
+// dq_reduce_kernel in a fixed order.  Needs D % 8 == 0 and 16-byte aligned rows.
+struct LayerNormBwdParams {
+  const __nv_bfloat16* grad;   // [N,D], row stride grad_row_stride, feature stride 1
+  int64_t grad_row_stride;
+  const __nv_bfloat16* x;      // [N,D] contiguous: the forward's BF16 output
+  const float* stats;          // [2,N]: mean, rstd
+  const float* weight;         // [D] or NULL (ones)
+  __nv_bfloat16* dx;           // [N,D] contiguous
+  float* partials;             // [gridDim.x, 2 D]
+  int64_t N;
+  int32_t D;
+};
+
+template <int NJ, int T>
+__global__ void __launch_bounds__(T)
+layer_norm_bwd_kernel(const __grid_constant__ LayerNormBwdParams p) {
+  constexpr int NW = T / 32;
+  __shared__ float scratch[2 * 2 * NW];
+  const int tid = threadIdx.x;
+  const int D = p.D;
+  float w[NJ][8], dw[NJ][8], db[NJ][8];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int c = j * T + tid;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      w[j][e] = (c * 8 < D && p.weight != nullptr) ? p.weight[c * 8 + e] : 1.f;
+      dw[j][e] = 0.f;
+      db[j][e] = 0.f;
+    }
+  }
+  const float inv_width = 1.0f / (float)D;
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < p.N; row += gridDim.x) {
+    const float mean = p.stats[row], rstd = p.stats[p.N + row];
+    float g[NJ][8], xhat[NJ][8];
+    float sums[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int c = j * T + tid;
+      if (c * 8 < D) {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.grad + row * p.grad_row_stride) + c), g[j]);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + row * (int64_t)D) + c), xhat[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xhat[j][e] = (xhat[j][e] - mean) * rstd;
+          const float gw = g[j][e] * w[j][e];
+          sums[0] += gw;
+          sums[1] = fmaf(gw, xhat[j][e], sums[1]);
+          dw[j][e] = fmaf(g[j][e], xhat[j][e], dw[j][e]);
+          db[j][e] += g[j][e];
+        }
+      }
+    }
+    block_sum<2, T>(sums, scratch, parity, tid);
+    const float mean_gw = sums[0] * inv_width, mean_gwx = sums[1] * inv_width;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int c = j * T + tid;
+      if (c * 8 < D) {
+        float dx[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          dx[e] = rstd * (g[j][e] * w[j][e] - mean_gw - xhat[j][e] * mean_gwx);
+        *(reinterpret_cast<uint4*>(p.dx + row * (int64_t)D) + c) = pack8(dx);
+      }
+    }
+  }
+  float* prow = p.partials + (int64_t)blockIdx.x * (2 * D);
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int c = j * T + tid;
+    if (c * 8 < D) {
+      float4* wdst = reinterpret_cast<float4*>(prow + c * 8);
+      float4* bdst = reinterpret_cast<float4*>(prow + D + c * 8);
+      wdst[0] = make_float4(dw[j][0], dw[j][1], dw[j][2], dw[j][3]);
+      wdst[1] = make_float4(dw[j][4], dw[j][5], dw[j][6], dw[j][7]);
+      bdst[0] = make_float4(db[j][0], db[j][1], db[j][2], db[j][3]);
+      bdst[1] = make_float4(db[j][4], db[j][5], db[j][6], db[j][7]);
+    }
+  }
+}
+
 // Second stage of the query gradient: column sums of the [rows, R] partials in a fixed
 // order, so the result is bit-identical from call to call.  A CTA owns 16 columns (one
 // 64-byte segment of every row); its 32 row groups each add every 32nd row, four rows at a

@@ -155,6 +155,31 @@ int attnres_b200_forward_layer_norm(
     uint32_t flags, void* stream);
 
 /*
+ * Backward of the LayerNorm that attnres_b200_forward_layer_norm applies, from what that
+ * forward wrote (no counterpart in the reference, which runs a separate LayerNorm and leaves
+ * its backward to the framework):
+ *
+ *   grad_normed       device BF16 [N,D], row stride `grad_row_stride`, feature stride 1
+ *   out, norm_stats   as written by the forward; norm_weight as passed to it (NULL = ones)
+ *   grad_out          device BF16 [N,D] contiguous: the gradient with respect to `out`
+ *                     (add any gradient that reaches `out` directly, then hand the sum to
+ *                     attnres_b200_backward as its `grad_out`)
+ *   partials          device FP32 workspace [partial_rows, 2 D], partial_rows >=
+ *                     attnres_b200_layer_norm_workspace_rows(N, D, device)
+ *   grad_weight_bias  device FP32 [2 D]: the weight gradient, then the bias gradient, summed
+ *                     in a fixed order
+ *
+ * Needs D % 8 == 0 and 16-byte aligned rows (ATTNRES_B200_ERR_MISALIGNED otherwise; a caller
+ * with another layout computes the LayerNorm backward itself).
+ */
+int32_t attnres_b200_layer_norm_workspace_rows(int64_t N, int32_t D, int32_t device);
+int attnres_b200_layer_norm_backward(
+    const void* grad_normed, int64_t grad_row_stride, const void* out, const float* norm_stats,
+    const float* norm_weight, int64_t N, int32_t D,
+    void* grad_out, float* partials, int32_t partial_rows, float* grad_weight_bias,
+    void* stream);
+
+/*
  * 1 when the backward of this shape (aligned layout assumed) is faster with the forward's
  * output and residual (it then finishes every source in one pass instead of staging the
  * whole position in shared memory), 0 otherwise.  Pure host function; plays the role of the

@@ -163,3 +163,20 @@ def test_kernel_family_selection_is_a_pure_host_decision():
     assert _native.kernel_family(49, 4096, 4096, True, False) == "tma"
     assert _native.kernel_family(2, 1024, 1024, False, False) == "generic"
     assert _native.kernel_family(0, 1024, 1024, True, False) == "invalid"
+
+
+def test_layer_norm_backward_entry_point_checks_its_arguments():
+    lib = _native.load()
+
+    def call(grad=0x1000, stride=16, out=0x2000, stats=0x3000, N=4, D=16, dx=0x4000,
+             partials=0x5000, rows=4, both=0x6000):
+        return lib.attnres_b200_layer_norm_backward(grad, stride, out, stats, None, N, D, dx,
+                                                    partials, rows, both, None)
+
+    assert call(D=0) == 3 and call(D=8200) == 3
+    assert call(N=0) == 5
+    assert call(grad=None) == 1 and call(both=None) == 1
+    assert call(D=12) == 7            # rows of 12 features cannot be read 16 bytes at a time
+    assert call(grad=0x1008) == 7 and call(stride=12) == 7
+    assert lib.attnres_b200_layer_norm_workspace_rows(0, 16, 0) == -5
+    assert lib.attnres_b200_layer_norm_workspace_rows(4, 0, 0) == -3

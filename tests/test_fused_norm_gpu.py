@@ -127,3 +127,29 @@ def test_fused_layer_norm_c_abi_writes_only_its_outputs():
                                    rtol=1e-4, atol=1e-5)
         torch.testing.assert_close(normed.view(n, d).float(),
                                    F.layer_norm(x, (d,), weight, bias, 1e-5), rtol=2**-7, atol=2**-7)
+
+
+@pytest.mark.parametrize("rows,width", [(37, 1024), (300, 2048), (129, 4096), (65, 8192), (500, 256),
+                                        (33, 3000)])
+def test_layer_norm_backward_kernel_matches_the_framework(rows, width):
+    """The library's LayerNorm-backward kernel (the backward of the fused epilogue) against
+    autograd through F.layer_norm on the same BF16 read, for a contiguous and a strided
+    upstream gradient."""
+    from attnres.fused import layer_norm_backward
+    torch.manual_seed(7)
+    x = torch.randn(rows, width, device="cuda", dtype=BF16)
+    weight = 1.0 + 0.1 * torch.randn(width, device="cuda")
+    bias = 0.1 * torch.randn(width, device="cuda")
+    mean = x.float().mean(-1)
+    rstd = torch.rsqrt(x.float().var(-1, unbiased=False) + 1e-5)
+    stats = torch.stack((mean, rstd)).contiguous()
+    for grad in (torch.randn(rows, width, device="cuda", dtype=BF16),
+                 torch.randn(rows, width + 8, device="cuda", dtype=BF16)[:, :width]):
+        leaf = x.float().requires_grad_()
+        w, b = weight.clone().requires_grad_(), bias.clone().requires_grad_()
+        F.layer_norm(leaf, (width,), w, b, 1e-5).backward(grad.float())
+        through, grad_weight, grad_bias = layer_norm_backward(grad, x, stats, weight)
+        assert through.dtype == BF16 and grad_weight.dtype == torch.float32
+        torch.testing.assert_close(through.float(), leaf.grad, rtol=2**-7, atol=2**-7)
+        torch.testing.assert_close(grad_weight, w.grad, rtol=1e-3, atol=1e-3 * float(w.grad.abs().max()))
+        torch.testing.assert_close(grad_bias, b.grad, rtol=1e-3, atol=1e-3 * float(b.grad.abs().max()))
