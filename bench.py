@@ -905,6 +905,48 @@ def run_single_cell(args) -> None:
         extra = {"bwd_then_add_ms": a, "bwd_accumulate_ms": fu, "accumulate_speedup": a / fu,
                  "bwd_accumulate_gbs": acc_bytes / fu / 1e6,
                  "bwd_accumulate_frac": acc_bytes / fu / 1e6 / peak}
+    if args.fused_norm:
+        # The read with the LayerNorm of the next sublayer in its epilogue (one more [N,D] BF16
+        # row written), and the LayerNorm backward kernel that precedes the read's backward.
+        weight = torch.ones(width, device=device, dtype=torch.float32)
+        bias = torch.zeros(width, device=device, dtype=torch.float32)
+        normed = torch.empty_like(out)
+        norm_stats = torch.empty(2, rows, device=device, dtype=torch.float32)
+        through = torch.empty_like(out)
+        ln_rows = _native.layer_norm_workspace_rows(rows, width, 0)
+        ln_partials = torch.empty(ln_rows, 2 * width, device=device, dtype=torch.float32)
+        both = torch.empty(2 * width, device=device, dtype=torch.float32)
+        norm_fwd_ms, norm_bwd_ms = [], []
+        for index in range(args.warmup + args.steps):
+            flush.zero_()
+            n0, n1, n2, n3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+            n0.record()
+            _native.forward_layer_norm(src, [width] * sources, [1] * sources, sources, rows, width,
+                                       rank, query.data_ptr(), 1, 2**-23, scale, out.data_ptr(),
+                                       width, logits.data_ptr(), stats.data_ptr(),
+                                       weight.data_ptr(), bias.data_ptr(), 1e-5,
+                                       normed.data_ptr(), norm_stats.data_ptr(), flags, stream,
+                                       residual_ptr=saved.get("residual_ptr"))
+            n1.record()
+            flush.zero_()
+            n2.record()
+            _native.check(_native.layer_norm_backward(
+                upstream.data_ptr(), width, out.data_ptr(), norm_stats.data_ptr(),
+                weight.data_ptr(), rows, width, through.data_ptr(), ln_partials.data_ptr(),
+                ln_rows, both.data_ptr(), stream), "attnres_b200_layer_norm_backward")
+            n3.record()
+            torch.cuda.synchronize()
+            if index >= args.warmup:
+                norm_fwd_ms.append(n0.elapsed_time(n1))
+                norm_bwd_ms.append(n2.elapsed_time(n3))
+        nf = sorted(norm_fwd_ms)[len(norm_fwd_ms) // 2]
+        nb = sorted(norm_bwd_ms)[len(norm_bwd_ms) // 2]
+        norm_fwd_bytes = fwd_bytes + rows * 2 * width        # + the normalised row
+        norm_bwd_bytes = rows * 6 * width                    # gradient and read in, gradient out
+        extra.update({"fwd_layer_norm_ms": nf, "fwd_layer_norm_gbs": norm_fwd_bytes / nf / 1e6,
+                      "fwd_layer_norm_frac": norm_fwd_bytes / nf / 1e6 / peak,
+                      "layer_norm_bwd_ms": nb, "layer_norm_bwd_gbs": norm_bwd_bytes / nb / 1e6,
+                      "layer_norm_bwd_frac": norm_bwd_bytes / nb / 1e6 / peak})
     print(json.dumps({"cell": [sources, rows, width, rank], "fwd_ms": f, "bwd_ms": b, **extra,
                       "fwd_gbs": fwd_bytes / f / 1e6, "bwd_gbs": bwd_bytes / b / 1e6,
                       "fwd_frac": fwd_bytes / f / 1e6 / peak, "bwd_frac": bwd_bytes / b / 1e6 / peak,
@@ -944,6 +986,9 @@ def main() -> None:
                         help="--cell: save the output residual and prefer the one-pass backward")
     parser.add_argument("--accumulate", action="store_true",
                         help="--cell: also time the backward that adds into running gradient buffers")
+    parser.add_argument("--fused-norm", action="store_true",
+                        help="--cell: also time the read with the LayerNorm epilogue and the "
+                             "LayerNorm backward kernel")
     parser.add_argument("--two-pass", action="store_true",
                         help="--cell: never save the output residual (staged backward)")
     parser.add_argument("--strong", action="store_true",

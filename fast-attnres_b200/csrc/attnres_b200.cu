@@ -573,11 +573,33 @@ extern "C" int attnres_b200_selftest_wait_limit(const void* scratch16, uint64_t 
 // Backward of the fused LayerNorm epilogue.
 
 namespace {
-constexpr int kLayerNormRowsPerSm = 8;
+// Instance per width class, from timing the candidates on 16 384-row inputs: rows per
+// iteration (B), ring stages (K), and the CTAs an SM holds (registers and ring bytes).
+struct LayerNormBwdPlan {
+  int rows_per_iteration;
+  int ctas_per_sm;
+};
 
-template <int NJ, int T>
+inline LayerNormBwdPlan layer_norm_bwd_plan(int D) {
+  if (D <= 1024) return {2, 6};   // <2, 64, 2, 4>
+  if (D <= 2048) return {2, 3};   // <2, 128, 2, 2>
+  if (D <= 4096) return {2, 2};   // <4, 128, 2, 2>
+  return {1, 1};                  // <4, 256, 1, 3>
+}
+
+inline int layer_norm_bwd_grid(int64_t N, int D, int sms) {
+  const LayerNormBwdPlan plan = layer_norm_bwd_plan(D);
+  const int64_t iterations = (N + plan.rows_per_iteration - 1) / plan.rows_per_iteration;
+  const int64_t cap = (int64_t)sms * plan.ctas_per_sm;
+  return (int)(iterations < cap ? iterations : cap);
+}
+
+template <int NJ, int T, int B, int K>
 int launch_layer_norm_bwd(const LayerNormBwdParams& p, int grid, cudaStream_t stream) {
-  layer_norm_bwd_kernel<NJ, T><<<grid, T, 0, stream>>>(p);
+  static SmemGrant grant;
+  constexpr uint32_t smem = LayerNormBwdRing<NJ, T, B, K>::kBytes;
+  if (int st = prepare_kernel(layer_norm_bwd_kernel<NJ, T, B, K>, smem, grant)) return st;
+  layer_norm_bwd_kernel<NJ, T, B, K><<<grid, T, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? ATTNRES_B200_OK : ATTNRES_B200_ERR_CUDA;
 }
 }  // namespace
@@ -587,8 +609,7 @@ extern "C" int32_t attnres_b200_layer_norm_workspace_rows(int64_t N, int32_t D, 
   if (N < 1) return -ATTNRES_B200_ERR_BAD_ROWS;
   int sms = 0;
   if (int st = sm_count(device, &sms)) return -st;
-  const int64_t cap = (int64_t)sms * kLayerNormRowsPerSm;
-  return (int32_t)(N < cap ? N : cap);
+  return layer_norm_bwd_grid(N, D, sms);
 }
 
 extern "C" int attnres_b200_layer_norm_backward(
@@ -607,8 +628,7 @@ extern "C" int attnres_b200_layer_norm_backward(
   int device = 0, sms = 0;
   if (int st = current_device(&device)) return st;
   if (int st = sm_count(device, &sms)) return st;
-  const int64_t cap = (int64_t)sms * kLayerNormRowsPerSm;
-  const int grid = (int)(N < cap ? N : cap);
+  const int grid = layer_norm_bwd_grid(N, D, sms);
   if (partial_rows < grid) return ATTNRES_B200_ERR_WORKSPACE;
   LayerNormBwdParams p;
   p.grad = static_cast<const __nv_bfloat16*>(grad_normed);
@@ -622,10 +642,10 @@ extern "C" int attnres_b200_layer_norm_backward(
   p.D = D;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   int st;
-  if (D <= 1024) st = launch_layer_norm_bwd<1, 128>(p, grid, cs);
-  else if (D <= 2048) st = launch_layer_norm_bwd<1, 256>(p, grid, cs);
-  else if (D <= 4096) st = launch_layer_norm_bwd<2, 256>(p, grid, cs);
-  else st = launch_layer_norm_bwd<4, 256>(p, grid, cs);
+  if (D <= 1024) st = launch_layer_norm_bwd<2, 64, 2, 4>(p, grid, cs);
+  else if (D <= 2048) st = launch_layer_norm_bwd<2, 128, 2, 2>(p, grid, cs);
+  else if (D <= 4096) st = launch_layer_norm_bwd<4, 128, 2, 2>(p, grid, cs);
+  else st = launch_layer_norm_bwd<4, 256, 1, 3>(p, grid, cs);
   if (st != ATTNRES_B200_OK) return st;
   const int columns = 2 * D;
   dq_reduce_kernel<<<(columns + kDqReduceColumns - 1) / kDqReduceColumns,

@@ -398,12 +398,78 @@ struct LayerNormBwdParams {
   int32_t D;
 };
 
-template <int NJ, int T>
+// Shared-memory ring of the LayerNorm backward: K stages of B rows.  A thread copies and reads
+// back only its own 16-byte chunks (cp.async, no barrier needed for them); lane 0 of every warp
+// copies the rows' (mean, rstd) for its warp.
+template <int NJ, int T, int B, int K>
+struct LayerNormBwdRing {
+  static constexpr int kChunks = K * B * 2 * NJ * T;          // uint4 each
+  static constexpr int kStats = K * B * 2 * (T / 32);         // float each
+  static constexpr uint32_t kBytes = kChunks * 16u + kStats * 4u;
+};
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                   (uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// Starts the copies of rows base .. base+B-1 into `stage` and closes the group (also when
+// nothing was copied, so that every iteration adds exactly one group).  Rows at or beyond N
+// become zeros with rstd = 0: they add nothing to any sum.
+template <int NJ, int T, int B, int K>
+__device__ __forceinline__ void layer_norm_bwd_issue(const LayerNormBwdParams& p, int64_t base,
+                                                     int stage, int tid, uint4* chunks,
+                                                     float* stats) {
+  constexpr int NW = T / 32;
+  const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const int64_t row = base + b;
+    const bool valid = row < p.N;
+    if (lane == 0) {
+      float* dst = stats + ((stage * B + b) * 2) * NW + warp;
+      if (valid) {
+        cp_async_4(dst, p.stats + row);
+        cp_async_4(dst + NW, p.stats + p.N + row);
+      } else {
+        dst[0] = 0.f;
+        dst[NW] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int c = j * T + tid;
+      uint4* dst = chunks + (((stage * B + b) * 2) * NJ + j) * T + tid;
+      if (valid && c * 8 < p.D) {
+        cp_async_16(dst, reinterpret_cast<const uint4*>(p.grad + row * p.grad_row_stride) + c);
+        cp_async_16(dst + NJ * T, reinterpret_cast<const uint4*>(p.x + row * (int64_t)p.D) + c);
+      } else {
+        dst[0] = make_uint4(0u, 0u, 0u, 0u);
+        dst[NJ * T] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// B rows per iteration share one CTA-wide reduction, and the rows of the next K-1 iterations
+// are on their way into the ring while the current ones are reduced and stored: the kernel is
+// bound by how many bytes an SM keeps in flight, not by arithmetic.
+template <int NJ, int T, int B, int K>
 __global__ void __launch_bounds__(T)
 layer_norm_bwd_kernel(const __grid_constant__ LayerNormBwdParams p) {
   constexpr int NW = T / 32;
-  __shared__ float scratch[2 * 2 * NW];
-  const int tid = threadIdx.x;
+  using Ring = LayerNormBwdRing<NJ, T, B, K>;
+  extern __shared__ __align__(16) unsigned char ring_bytes[];
+  uint4* chunks = reinterpret_cast<uint4*>(ring_bytes);
+  float* ring_stats = reinterpret_cast<float*>(ring_bytes + Ring::kChunks * 16);
+  __shared__ float scratch[2 * 2 * B * NW];
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int D = p.D;
   float w[NJ][8], dw[NJ][8], db[NJ][8];
 #pragma unroll
@@ -417,42 +483,71 @@ layer_norm_bwd_kernel(const __grid_constant__ LayerNormBwdParams p) {
     }
   }
   const float inv_width = 1.0f / (float)D;
-  int parity = 0;
-  for (int64_t row = blockIdx.x; row < p.N; row += gridDim.x) {
-    const float mean = p.stats[row], rstd = p.stats[p.N + row];
-    float g[NJ][8], xhat[NJ][8];
-    float sums[2] = {0.f, 0.f};
+  const int64_t stride = (int64_t)gridDim.x * B;
+  const int64_t first = (int64_t)blockIdx.x * B;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int c = j * T + tid;
-      if (c * 8 < D) {
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.grad + row * p.grad_row_stride) + c), g[j]);
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + row * (int64_t)D) + c), xhat[j]);
+  for (int k = 0; k < K - 1; ++k)
+    layer_norm_bwd_issue<NJ, T, B, K>(p, first + k * stride, k, tid, chunks, ring_stats);
+  int parity = 0, stage = 0;
+  for (int64_t base = first; base < p.N; base += stride) {
+    // refills the stage that the previous iteration read (its reads came before that
+    // iteration's CTA barrier)
+    layer_norm_bwd_issue<NJ, T, B, K>(p, base + (K - 1) * stride, stage == 0 ? K - 1 : stage - 1,
+                                      tid, chunks, ring_stats);
+    asm volatile("cp.async.wait_group %0;" ::"n"(K - 1) : "memory");
+    __syncwarp();
+    uint4 gq[B][NJ], xq[B][NJ];
+    float mean[B], rstd[B], sums[2 * B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      mean[b] = ring_stats[((stage * B + b) * 2) * NW + warp];
+      rstd[b] = ring_stats[((stage * B + b) * 2 + 1) * NW + warp];
+      sums[2 * b] = 0.f;
+      sums[2 * b + 1] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const uint4* src = chunks + (((stage * B + b) * 2) * NJ + j) * T + tid;
+        gq[b][j] = src[0];
+        xq[b][j] = src[NJ * T];
+        float g[8], xhat[8];
+        unpack8(gq[b][j], g);
+        unpack8(xq[b][j], xhat);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          xhat[j][e] = (xhat[j][e] - mean) * rstd;
-          const float gw = g[j][e] * w[j][e];
-          sums[0] += gw;
-          sums[1] = fmaf(gw, xhat[j][e], sums[1]);
-          dw[j][e] = fmaf(g[j][e], xhat[j][e], dw[j][e]);
-          db[j][e] += g[j][e];
+          xhat[e] = (xhat[e] - mean[b]) * rstd[b];
+          const float gw = g[e] * w[j][e];
+          sums[2 * b] += gw;
+          sums[2 * b + 1] = fmaf(gw, xhat[e], sums[2 * b + 1]);
+          dw[j][e] = fmaf(g[e], xhat[e], dw[j][e]);
+          db[j][e] += g[e];
         }
       }
     }
-    block_sum<2, T>(sums, scratch, parity, tid);
-    const float mean_gw = sums[0] * inv_width, mean_gwx = sums[1] * inv_width;
+    block_sum<2 * B, T>(sums, scratch, parity, tid);
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int c = j * T + tid;
-      if (c * 8 < D) {
-        float dx[8];
+    for (int b = 0; b < B; ++b) {
+      if (base + b < p.N) {
+        const float mean_gw = sums[2 * b] * inv_width, mean_gwx = sums[2 * b + 1] * inv_width;
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          dx[e] = rstd * (g[j][e] * w[j][e] - mean_gw - xhat[j][e] * mean_gwx);
-        *(reinterpret_cast<uint4*>(p.dx + row * (int64_t)D) + c) = pack8(dx);
+        for (int j = 0; j < NJ; ++j) {
+          const int c = j * T + tid;
+          if (c * 8 < D) {
+            float g[8], xhat[8], dx[8];
+            unpack8(gq[b][j], g);
+            unpack8(xq[b][j], xhat);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              xhat[e] = (xhat[e] - mean[b]) * rstd[b];
+              dx[e] = rstd[b] * (g[e] * w[j][e] - mean_gw - xhat[e] * mean_gwx);
+            }
+            *(reinterpret_cast<uint4*>(p.dx + (base + b) * (int64_t)D) + c) = pack8(dx);
+          }
+        }
       }
     }
+    stage = stage + 1 == K ? 0 : stage + 1;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   float* prow = p.partials + (int64_t)blockIdx.x * (2 * D);
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {

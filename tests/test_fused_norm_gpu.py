@@ -130,7 +130,10 @@ def test_fused_layer_norm_c_abi_writes_only_its_outputs():
 
 
 @pytest.mark.parametrize("rows,width", [(37, 1024), (300, 2048), (129, 4096), (65, 8192), (500, 256),
-                                        (33, 3000)])
+                                        (33, 3000),
+                                        # more rows than one pass of the grid: every CTA goes
+                                        # round its shared-memory ring more than once
+                                        (9001, 1024), (3001, 2048), (2001, 4096), (701, 8192)])
 def test_layer_norm_backward_kernel_matches_the_framework(rows, width):
     """The library's LayerNorm-backward kernel (the backward of the fused epilogue) against
     autograd through F.layer_norm on the same BF16 read, for a contiguous and a strided
