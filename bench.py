@@ -363,6 +363,58 @@ def time_sweep(cells, rows, steps, warmup, flat32, flat16, distributed, device, 
     return total_ms / steps, fwd_ms, bwd_ms, own_ms, tail_ms
 
 
+COPY_PIECE_ELEMS = 128 * 1024 * 1024      # BF16 elements per memcpy of the calibration copies
+
+
+def time_same_size_copies(cells, grad_buffer, steps, warmup):
+    """A plain device-to-device copy that moves as many bytes as each cell's forward and each
+    cell's backward (half read, half written), replayed and timed exactly like the sweep: one
+    CUDA graph per copy, the forward-sized copies in cell order, the backward-sized ones in
+    reverse, CUDA events around every replay.  The copy bandwidth a short launch reaches is
+    well below the large-copy peak (launch, ramp-up and tail are a fixed cost), so this is what
+    the small cells' rates are to be read against.  A copy is issued in pieces of 256 MiB: one
+    device-to-device memcpy of more than about 500 MB ran at 2.9 TB/s on B200 (0.45 of what the
+    smaller ones reach), which would be no yardstick.  Returns per cell (forward-sized copy
+    GB/s, backward-sized copy GB/s)."""
+    plans = []
+    for cell in cells:
+        source = cell.values.view(-1)
+        graphs = []
+        for total in (cell.fwd_bytes, cell.bwd_bytes):
+            elems = min(total // 4, source.numel())       # 2 B read + 2 B written per element
+            src, dst = source[:elems], grad_buffer[:elems]
+
+            def copy_in_pieces():
+                for begin in range(0, elems, COPY_PIECE_ELEMS):
+                    dst[begin:begin + COPY_PIECE_ELEMS].copy_(src[begin:begin + COPY_PIECE_ELEMS])
+
+            copy_in_pieces()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                copy_in_pieces()
+            graphs.append((graph, elems * 4))
+        plans.append(graphs)
+    totals = [[0.0, 0.0] for _ in cells]
+    for iteration in range(warmup + steps):
+        events = [[None, None] for _ in cells]
+        for which, order in ((0, range(len(cells))), (1, reversed(range(len(cells))))):
+            for index in order:
+                first, last = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+                first.record()
+                plans[index][which][0].replay()
+                last.record()
+                events[index][which] = (first, last)
+        torch.cuda.synchronize()
+        if iteration >= warmup:
+            for index in range(len(cells)):
+                for which in (0, 1):
+                    first, last = events[index][which]
+                    totals[index][which] += first.elapsed_time(last) / steps
+    return [(plans[i][0][1] / (totals[i][0] * 1e-3) / 1e9, plans[i][1][1] / (totals[i][1] * 1e-3) / 1e9)
+            for i in range(len(cells))]
+
+
 def gather_floats(value: float, device, world: int) -> list[float]:
     import torch.distributed as dist
     if world == 1:
@@ -411,6 +463,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
     value = tokens_per_step / (ms_per_step * 1e-3)
     rank_kernel_ms = gather_floats(own_ms, device, world)
     rank_tail_ms = gather_floats(tail_ms, device, world)
+
+    copies = None if distributed else time_same_size_copies(cells, grad_buffer, args.steps, args.warmup)
 
     strong = None
     if distributed:
@@ -472,6 +526,18 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
             "frac_of_peak": round((cell.fwd_bytes + cell.bwd_bytes) / ((f + b) * 1e-3) / 1e9 / peak, 4),
             "backward_kernel": cell.family,
         })
+    same_size = None
+    if copies is not None:
+        copy_ms = 0.0
+        for entry, cell, f, b, (copy_f, copy_b) in zip(per_cell, cells, fwd_ms, bwd_ms, copies):
+            entry["copy_gbs_fwd_size"], entry["copy_gbs_bwd_size"] = round(copy_f, 1), round(copy_b, 1)
+            entry["fwd_vs_copy"] = round(cell.fwd_bytes / (f * 1e-3) / 1e9 / copy_f, 4)
+            entry["bwd_vs_copy"] = round(cell.bwd_bytes / (b * 1e-3) / 1e9 / copy_b, 4)
+            copy_ms += cell.fwd_bytes / (copy_f * 1e9) * 1e3 + cell.bwd_bytes / (copy_b * 1e9) * 1e3
+        same_size = {"ms_per_step_of_copies": copy_ms,
+                     "kernels_vs_copies": copy_ms / (sum(fwd_ms) + sum(bwd_ms)),
+                     "note": "plain device-to-device copies moving each launch's algorithmic "
+                             "bytes, replayed and timed like the sweep; per cell in `cells`"}
     # The CPU oracle is timed at N = 1 only (the reference arm reports it at every N).
     run_cpu = not args.skip_cpu and world == 1
     if run_cpu:
@@ -511,6 +577,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int) -> None:
                           "FP32 all-reduce of the 43 008 query-gradient floats plus the BF16 "
                           "cast, including the wait for the slowest rank"},
         "strong": strong,
+        "same_size_copy": same_size,
         "wait_gave_up_flag": gave_up,
         "cells": per_cell,
     }

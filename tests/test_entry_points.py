@@ -32,7 +32,7 @@ def test_bench_algorithmic_bytes_and_peak():
     forward, backward = bench.algorithmic_bytes(49, 16384, 4096)
     assert forward == 16384 * (2 * 49 * 4096 + 2 * 4096)
     assert backward == 16384 * (4 * 49 * 4096 + 2 * 4096)
-    assert forward + backward == 16384 * 1220608          # the survey's worked example
+    assert forward + backward == 16384 * 1220608          # 6SD + 4D bytes per position
     peak, kind = bench.measured_peak_gbs()
     assert peak > 1000 and kind in ("measured", "fallback")
     ratios = bench.traffic_ratios()

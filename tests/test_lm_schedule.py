@@ -25,7 +25,7 @@ def test_full_schedule_reads_every_earlier_output():
     config = lm.LMConfig(layers=24, width=1024, heads=16, ffn=4096, mode="full")
     counts = lm.read_source_counts(config)
     assert counts == tuple(range(2, 50)) and len(counts) == 48 and sum(counts) == 1224
-    # the survey's figure for the 24-layer step: 126.4 GB of AttnRes traffic at 16 384 rows
+    # the 24-layer Full-schedule step (S = 2..49, D = 1024): 126.4 GB of AttnRes traffic at 16 384 rows
     assert abs(lm.attnres_algorithmic_bytes(config, 16384) / 1e9 - 126.4) < 0.1
 
 
