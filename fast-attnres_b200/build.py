@@ -44,8 +44,10 @@ def build(*, force: bool = False, verbose: bool = False) -> Path:
     if not force and up_to_date():
         return OUTPUT
     OUTPUT.parent.mkdir(parents=True, exist_ok=True)
-    command = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
-               *map(str, SOURCES), "-o", str(OUTPUT)]
+    # ptxas always reports registers and spills (shown only when asked for): the flag also
+    # fixes the order in which it lays the kernels out, so every build of the same sources
+    # gives the same binary whether or not the report is printed.
+    command = [_nvcc(), *NVCC_FLAGS, "-Xptxas", "-v", *map(str, SOURCES), "-o", str(OUTPUT)]
     result = subprocess.run(command, capture_output=True, text=True)
     if verbose or result.returncode != 0:
         sys.stderr.write(result.stdout + result.stderr)
